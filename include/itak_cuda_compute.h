@@ -1,0 +1,247 @@
+/*
+ * itak_cuda_compute.h - C ABI of the B200 (sm_100a) KV-cache hot path.
+ *
+ * This is the boundary a `crates/cuda-compute` backend crate binds over FFI to
+ * implement the engine's `Compute::attention` step with backend-owned KV, the
+ * speculation seam (checkpoint / rewind / release) and the prefix-KV seam
+ * (snapshot capture / install).  Plain pointers and sizes only; no C++ or
+ * torch types cross it.  Each entry point names the reference interface it
+ * stands in for (paths relative to the reference repository root).
+ *
+ * Conventions
+ *  - Every call returns an itk_status.  0 is success; every refusal is a named
+ *    code mirroring one variant of the reference's error enums, and the text of
+ *    the last refusal is available from itk_last_error().  A refused call
+ *    leaves the backend's state exactly as it was (validate, then mutate).
+ *  - A backend owns `n_slots` resident sequences ("slots").  Calls on one
+ *    backend are serialised by the caller (the reference backend is not Sync).
+ *  - Rows arrive already RoPE'd: RoPE is the caller's job, as in
+ *    crates/attention/src/attention.rs:5-8.
+ *  - "host" pointers may be pageable or pinned; "device" pointers must be
+ *    device memory on the backend's device, 16-byte aligned.
+ *  - There is no CPU fallback: every data-path call launches CUDA kernels and
+ *    fails with ITK_ERR_CUDA when no device is usable.
+ */
+#ifndef ITAK_CUDA_COMPUTE_H
+#define ITAK_CUDA_COMPUTE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Refusal codes.  1..14 mirror crates/attention/src/error.rs:9-127
+ * (AttentionError), 32..39 mirror crates/itak-kv/src/error.rs (KvError),
+ * 64 is the backend's own StepFailed{step, detail}
+ * (crates/cpu-compute/src/cpu.rs:28-33).  100+ have no counterpart: they are
+ * limits of a device-resident cache with a fixed allocation. */
+typedef enum itk_status {
+    ITK_OK = 0,
+    ITK_ERR_ZERO_DIMENSION = 1,
+    ITK_ERR_INVALID_WINDOW = 2,
+    ITK_ERR_SIZE_OVERFLOW = 3,
+    ITK_ERR_SHAPE_MISMATCH = 4,
+    ITK_ERR_INVALID_LAYER = 5,
+    ITK_ERR_OUT_OF_ORDER_POSITION = 6,
+    ITK_ERR_NON_DIVISIBLE_HEADS = 7,
+    ITK_ERR_NO_VISIBLE_KEYS = 8,
+    ITK_ERR_CHECKPOINT_BUSY = 9,
+    ITK_ERR_STALE_CHECKPOINT = 10,
+    ITK_ERR_CHECKPOINT_TOO_DEEP = 11,
+    ITK_ERR_CHECKPOINT_RANGE_EXCEEDED = 12,
+    ITK_ERR_BULK_RESTORE_NOT_FRESH = 13,
+    ITK_ERR_REWIND_OUT_OF_RANGE = 14,
+    ITK_ERR_INCOHERENT_CACHE = 32,
+    ITK_ERR_INCONSISTENT_SNAPSHOT = 33,
+    ITK_ERR_GEOMETRY_MISMATCH = 38,
+    ITK_ERR_STEP_FAILED = 64,
+    ITK_ERR_CUDA = 100,
+    ITK_ERR_INVALID_ARGUMENT = 101,
+    ITK_ERR_CAPACITY = 102,
+    ITK_ERR_INVALID_SLOT = 103
+} itk_status;
+
+typedef enum itk_kv_dtype {
+    ITK_KV_F32 = 0, /* the reference CPU cache's format (crates/attention/src/cache.rs:11-15) */
+    ITK_KV_F16 = 1  /* IEEE half, round-to-nearest-even on append, NaN -> sign|0x7e00
+                       (crates/wgpu-compute/src/kernels/k1_q4k_gemv.rs:285-329) */
+} itk_kv_dtype;
+
+/* Shape of one backend.  Stands in for the (GlimmerConfig -> CacheShape)
+ * binding of crates/cpu-compute/src/cpu.rs:171-244 plus the session limits of
+ * crates/wgpu-compute/src/session.rs:235-249. */
+typedef struct itk_config {
+    uint32_t n_layers;
+    const uint32_t* layer_window; /* per layer: 0 = global, w > 0 = sliding window of w; NULL = all global */
+    uint32_t q_heads;
+    uint32_t kv_heads;
+    uint32_t head_dim;
+    uint32_t n_slots;     /* resident sequences */
+    uint32_t max_context; /* positions a slot can hold on a global layer */
+    uint32_t chunk_cap;   /* most rows one attention call may carry per sequence; a windowed
+                             layer's ring holds window + chunk_cap positions */
+    int32_t kv_dtype;     /* itk_kv_dtype */
+    int32_t device;       /* CUDA device ordinal */
+} itk_config;
+
+typedef struct itk_backend itk_backend;   /* opaque */
+typedef struct itk_snapshot itk_snapshot; /* opaque, device-resident prefix snapshot */
+
+/* Receipt of a live checkpoint: crates/attention/src/cache.rs:229-273.
+ * `id` names the slot's cache instance, so a handle presented to another
+ * sequence (or after a reset) is stale by construction. */
+typedef struct itk_checkpoint {
+    uint64_t id;
+    uint64_t serial;
+    uint64_t base; /* position of every layer when the checkpoint was taken */
+    uint64_t max_round_tokens;
+} itk_checkpoint;
+
+/* Per-call counters (SessionStats, crates/wgpu-compute/src/session.rs:493-540). */
+typedef struct itk_stats {
+    uint64_t attention_calls;
+    uint64_t kernel_launches;
+    uint64_t rows_appended;
+    uint64_t kv_bytes_read; /* algorithmic: visible keys x Hkv x D x 2 x element size */
+    uint64_t prefix_captures;
+    uint64_t prefix_restores;
+    uint64_t last_splits; /* KV splits chosen by the last decode launch */
+} itk_stats;
+
+/* ---- lifetime ------------------------------------------------------------ */
+
+/* KvCache::new for every slot (crates/attention/src/cache.rs:327-371): same
+ * refusal order (empty layer list, zero kv heads, zero head dim, zero window,
+ * size overflow), then q_heads % kv_heads, then the device allocation. */
+int itk_backend_create(const itk_config* cfg, itk_backend** out);
+void itk_backend_destroy(itk_backend* b);
+/* Text of the last refusal on `b`; with b == NULL, of the last failed create. */
+const char* itk_last_error(const itk_backend* b);
+/* Work is issued on `cuda_stream` (a cudaStream_t) from now on; NULL = the
+ * backend's own stream.  The caller orders its own work against it. */
+int itk_set_stream(itk_backend* b, void* cuda_stream);
+int itk_synchronize(itk_backend* b);
+int itk_get_stats(const itk_backend* b, itk_stats* out);
+/* Per-kernel device timing, the counterpart of the reference's timestamp-query
+ * diagnostics (crates/wgpu-compute/src/timestamps.rs:1-140).  While enabled,
+ * every attention and append kernel launch is bracketed by a CUDA event pair on
+ * the launching stream (up to `capacity` pairs, created up front).
+ * itk_profile_read synchronises the stream and returns the summed kernel
+ * milliseconds and launch counts since the last enable; capacity 0 disables. */
+int itk_profile_enable(itk_backend* b, uint32_t capacity);
+int itk_profile_read(itk_backend* b, double* attention_ms, uint64_t* attention_launches, double* append_ms,
+                     uint64_t* append_launches);
+
+/* ---- the attention step ---------------------------------------------------- */
+
+/* Compute::attention for one sequence (crates/muse-glimmer/src/compute.rs:29-42,82;
+ * crates/cpu-compute/src/cpu.rs:506-655).  Host buffers: q [rows][q_heads*D],
+ * k and v [rows][kv_heads*D], out [rows][q_heads*D].  `position` is the
+ * caller's Cache::position(); a backend whose layer is elsewhere refuses with
+ * ITK_ERR_STEP_FAILED naming both positions (cpu.rs:565-581).  Appends the
+ * rows at position.., then attends each row causally (and within the window on
+ * sliding layers).  Returns after the result is in `out`. */
+int itk_attention(itk_backend* b, uint32_t slot, uint32_t layer, const float* q, size_t q_len, const float* k,
+                  size_t k_len, const float* v, size_t v_len, uint64_t position, float* out);
+
+/* The same step for `n_seqs` slots at once, `rows` rows each (continuous
+ * batching; the reference runs one OS thread and one backend per slot,
+ * crates/itak-engine/src/engine.rs:4-15).  q [n_seqs][rows][q_heads*D],
+ * k, v [n_seqs][rows][kv_heads*D], out like q.  Host buffers. */
+int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                        const uint64_t* positions, uint32_t rows, const float* q, const float* k, const float* v,
+                        float* out);
+
+/* As itk_attention_batch with q, k, v, out resident in device memory; returns
+ * once the work is queued on the backend's stream. */
+int itk_attention_batch_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                               const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
+                               const float* d_v, float* d_out);
+
+/* gqa_attention alone (crates/attention/src/attention.rs:104-215) over what a
+ * slot already holds: `rows` queries at query_positions[], host buffers.
+ * Refuses ITK_ERR_NO_VISIBLE_KEYS when a query sees nothing. */
+int itk_gqa_attention(itk_backend* b, uint32_t slot, uint32_t layer, const float* q, size_t q_len, uint32_t rows,
+                      const uint64_t* query_positions, float* out);
+
+/* ---- KvCache-level operations ------------------------------------------------ */
+
+/* KvCache::append (crates/attention/src/cache.rs:423-474): one position's K
+ * and V rows, host f32.  Same check order: k length, v length, live
+ * checkpoint range, layer, position == appended. */
+int itk_append(itk_backend* b, uint32_t slot, uint32_t layer, const float* k, size_t k_len, const float* v,
+               size_t v_len, uint64_t position);
+/* `rows` consecutive positions start.. in one call, host f32 [rows][kv_heads*D]. */
+int itk_append_rows(itk_backend* b, uint32_t slot, uint32_t layer, const float* k, const float* v, uint32_t rows,
+                    uint64_t start);
+/* The same append for `n_seqs` slots with device-resident f32 sources
+ * [n_seqs][rows][kv_heads*D] (prefill of a resident cache without a host round
+ * trip); slot i receives rows at starts[i]..  Queued on the backend's stream. */
+int itk_append_rows_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                           const uint64_t* starts, uint32_t rows, const float* d_k, const float* d_v);
+/* KvCache::next_position / stored_len (cache.rs:407-415). */
+int itk_next_position(const itk_backend* b, uint32_t slot, uint32_t layer, uint64_t* out);
+int itk_stored_len(const itk_backend* b, uint32_t slot, uint32_t layer, uint64_t* out);
+/* The gather behind KvCache::view (cache.rs:581-585, 836-904): the visible rows
+ * of one layer, oldest first, [rows][kv_heads][D] in the cache's element type
+ * (2 or 4 bytes each), copied to host buffers holding at least
+ * stored_len * kv_heads * D elements.  keys or values may be NULL. */
+int itk_view_gather(itk_backend* b, uint32_t slot, uint32_t layer, void* keys, void* values,
+                    uint64_t* first_position, uint64_t* rows);
+/* KvCache::restore_bulk (cache.rs:513-577): install rows for positions
+ * first_position.. on a fresh layer, host f32 [rows][kv_heads*D]. */
+int itk_restore_bulk(itk_backend* b, uint32_t slot, uint32_t layer, uint64_t first_position, const float* keys,
+                     size_t keys_len, const float* values, size_t values_len);
+/* CpuCompute::reset (crates/cpu-compute/src/cpu.rs:264-267) for one slot:
+ * drops the sequence, its checkpoint and its cache identity. */
+int itk_reset(itk_backend* b, uint32_t slot);
+
+/* ---- speculation seam ---------------------------------------------------------- */
+
+/* CpuCompute::cache_checkpoint / KvCache::checkpoint (cpu.rs:281-295,
+ * cache.rs:634-717).  On the device ring (window + chunk_cap rows, one more
+ * than the reference session's ring of crates/wgpu-compute/src/session.rs:235-249)
+ * a round of at most chunk_cap rows never overwrites a row that a later query
+ * or a later view can reach, so nothing is copied; a bound above chunk_cap on
+ * a model with sliding layers refuses with ITK_ERR_CHECKPOINT_TOO_DEEP. */
+int itk_cache_checkpoint(itk_backend* b, uint32_t slot, uint64_t max_round_tokens, itk_checkpoint* out);
+/* CpuCompute::cache_rewind / KvCache::rewind_to (cpu.rs:309-322, cache.rs:758-818):
+ * truncate every layer of the slot to `target` positions, target in
+ * [base, appended].  The checkpoint stays live. */
+int itk_cache_rewind(itk_backend* b, uint32_t slot, const itk_checkpoint* cp, uint64_t target);
+/* CpuCompute::cache_release / KvCache::release (cpu.rs:326-339, cache.rs:824-833). */
+int itk_cache_release(itk_backend* b, uint32_t slot, const itk_checkpoint* cp);
+
+/* ---- prefix-KV seam --------------------------------------------------------------- */
+
+/* ResidentSession::capture_prefix_snapshot / KvSnapshot::capture
+ * (crates/wgpu-compute/src/session.rs:4827-4887, crates/itak-kv/src/snapshot.rs:247-302):
+ * every layer's visible rows in absolute-position order, kept in device memory
+ * in the cache's element type.  Refuses layers at different positions. */
+int itk_snapshot_capture(itk_backend* b, uint32_t slot, itk_snapshot** out);
+/* ResidentSession::install_prefix_snapshot / KvSnapshot::restore
+ * (session.rs:4925-4971, snapshot.rs:321-334): validate the whole snapshot
+ * against the backend's geometry, then reset the slot and scatter the rows to
+ * their slots; the slot ends at position token_count. */
+int itk_snapshot_restore(itk_backend* b, uint32_t slot, const itk_snapshot* snap);
+void itk_snapshot_free(itk_snapshot* snap);
+uint64_t itk_snapshot_token_count(const itk_snapshot* snap);
+uint64_t itk_snapshot_payload_bytes(const itk_snapshot* snap);
+/* One layer block copied to host in the cache's element type,
+ * [rows][kv_heads][D]; either pointer may be NULL. */
+int itk_snapshot_layer_to_host(itk_backend* b, const itk_snapshot* snap, uint32_t layer, void* keys, void* values,
+                               uint64_t* first_position, uint64_t* rows);
+/* Build a device snapshot from host f32 rows in the layout of the ITKV format's
+ * layer blocks (crates/itak-kv/src/snapshot.rs:13-29): for each layer,
+ * first_position[l], rows[l], keys[l] and values[l] as [rows][kv_heads*D].
+ * Values are converted to the cache's element type as an append would. */
+int itk_snapshot_from_host_f32(itk_backend* b, uint64_t token_count, const uint64_t* first_position,
+                               const uint64_t* rows, const float* const* keys, const float* const* values,
+                               itk_snapshot** out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ITAK_CUDA_COMPUTE_H */

@@ -1,0 +1,130 @@
+// Device helpers shared by the attention kernels: PTX wrappers and the CTA
+// epilogue that turns per-split partial results into the final output.
+#pragma once
+
+#include "kernels.cuh"
+
+namespace itk {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// 16-byte asynchronous global -> shared copy that bypasses L1 (the cache is
+// streamed once per step).  src_bytes == 0 writes 16 zero bytes and reads nothing.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr)
+                 : "memory");
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col).
+// Fragment ownership, with g = lane / 4 and t = lane % 4:
+//   a[0] = A[g][2t..2t+1]      a[1] = A[g+8][2t..2t+1]
+//   a[2] = A[g][2t+8..2t+9]    a[3] = A[g+8][2t+8..2t+9]
+//   b0   = B[2t..2t+1][g]      b1   = B[2t+8..2t+9][g]
+//   c[0..1] = D[g][2t..2t+1]   c[2..3] = D[g+8][2t..2t+1]
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
+    return static_cast<uint32_t>(__half_as_ushort(lo)) | (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+}
+
+// x = hi + lo with hi = fp16(x) and lo = fp16(x - hi): two half operands that
+// together carry ~22 bits of x.  An f16 tensor-core product against an exact
+// f16 cache element then reproduces the f32 product to ~1e-7 relative.
+__device__ __forceinline__ void split_half(float x, __half& hi, __half& lo) {
+    hi = __float2half_rn(x);
+    lo = __float2half_rn(x - __half2float(hi));
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// CTA epilogue.  On entry the CTA's own result for its key range sits in shared
+// memory: fo[8][D] (unnormalised sum of p * v), fm[8] (running max, log2
+// domain, -inf when the range was empty) and fl[8] (sum of p).  With one split
+// the output is written directly.  Otherwise the partial goes to global
+// scratch, the CTA takes a ticket, and the CTA that draws the last ticket
+// merges every split (log-sum-exp) and writes the output; nobody waits.
+// The ticket counter is left at zero for the next launch.
+template <int THREADS>
+__device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t split,
+                                            uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
+                                            const float* fm, const float* fl, int* s_flag) {
+    const uint32_t tid = threadIdx.x;
+    const uint32_t HY = p.layer.kv_heads * p.gchunks;
+    float* out = p.out + (static_cast<size_t>(unit) * p.q_heads + head0) * D;
+    if (p.splits == 1) {
+        for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
+            const uint32_t h = idx / D;
+            out[idx] = fo[idx] / fl[h];
+        }
+        return;
+    }
+    const size_t cell = static_cast<size_t>(unit) * HY + hy;
+    float* po = p.part_o + (cell * p.splits + split) * (kHeadsPerCta * D);
+    float* pml = p.part_ml + (cell * p.splits + split) * (kHeadsPerCta * 2);
+    for (uint32_t idx = tid; idx < nh * D; idx += THREADS) po[idx] = fo[idx];
+    if (tid < nh) {
+        pml[2 * tid] = fm[tid];
+        pml[2 * tid + 1] = fl[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(p.tickets + cell, 1u);
+        *s_flag = (ticket == p.splits - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (*s_flag == 0) return;
+    __threadfence();
+    const float* all_o = p.part_o + cell * p.splits * (kHeadsPerCta * D);
+    const float* all_ml = p.part_ml + cell * p.splits * (kHeadsPerCta * 2);
+    for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
+        const uint32_t h = idx / D;
+        float M = -INFINITY, L = 0.f, O = 0.f;
+        for (uint32_t s = 0; s < p.splits; ++s) {
+            const float ms = __ldcg(all_ml + s * (kHeadsPerCta * 2) + 2 * h);
+            if (ms == -INFINITY) continue;
+            const float ls = __ldcg(all_ml + s * (kHeadsPerCta * 2) + 2 * h + 1);
+            const float os = __ldcg(all_o + static_cast<size_t>(s) * (kHeadsPerCta * D) + idx);
+            const float Mn = fmaxf(M, ms);
+            const float a = fast_exp2(M - Mn);  // exp2(-inf) = 0 on the first live split
+            const float b = fast_exp2(ms - Mn);
+            O = O * a + os * b;
+            L = L * a + ls * b;
+            M = Mn;
+        }
+        out[idx] = O / L;
+    }
+    if (tid == 0) p.tickets[cell] = 0u;
+}
+
+}  // namespace itk

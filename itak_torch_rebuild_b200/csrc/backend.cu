@@ -1,0 +1,1098 @@
+// Host side of the C ABI (include/itak_cuda_compute.h): the resident cache's
+// bookkeeping, every refusal in the reference's order and wording, and the
+// dispatch of the hot-path kernels.  The arithmetic lives in the kernels; this
+// file never touches a cache element on the CPU.
+//
+// State mirrored from the reference:
+//   - per (slot, layer) `appended`: KvCache's position counter
+//     (crates/attention/src/cache.rs:114-116, 407-415);
+//   - per slot one live checkpoint (cache id, serial, per-layer bases, round
+//     bound): crates/attention/src/cache.rs:229-321, 606-833;
+//   - the attention step's position cross-check against the caller's
+//     Cache::position(): crates/cpu-compute/src/cpu.rs:558-581.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/itak_cuda_compute.h"
+#include "kernels.cuh"
+
+namespace itk {
+cudaError_t configure_decode_f16();
+}
+
+namespace {
+
+using itk::AppendLaunch;
+using itk::AttnLaunch;
+using itk::CopyLaunch;
+using itk::SeqDesc;
+
+std::string g_create_error;
+std::atomic<uint64_t> g_next_cache_id{1};  // crates/attention/src/cache.rs:32
+
+std::string zu(uint64_t v) { return std::to_string(v); }
+
+struct SlotState {
+    uint64_t id = 0;
+    bool built = false;  // the reference builds its KV state lazily at the first forward
+    std::vector<uint64_t> appended;
+    bool live = false;
+    uint64_t next_serial = 0;
+    uint64_t live_serial = 0;
+    uint64_t max_round = 0;
+    std::vector<uint64_t> bases;
+};
+
+constexpr size_t kPartCellSplits = 148 * 64;  // (cell, split) partials the scratch holds
+
+}  // namespace
+
+struct itk_snapshot {
+    int device = 0;
+    bool f16 = false;
+    uint32_t kv_heads = 0, head_dim = 0;
+    std::vector<uint32_t> window;  // per layer, 0 = global
+    uint64_t token_count = 0;
+    std::vector<uint64_t> first, rows;  // per layer
+    std::vector<uint64_t> k_off, v_off;  // element offsets inside `data`
+    uint64_t total_elems = 0;
+    void* data = nullptr;
+};
+
+struct itk_backend {
+    itk_config cfg{};
+    std::vector<uint32_t> window, ring;
+    std::vector<size_t> layer_off;  // element offset of each layer inside a slab
+    size_t slab_elems = 0;
+    bool f16 = false;
+    uint32_t elem_bytes = 4;
+    uint32_t group = 1, gchunks = 1;
+    void* k_slab = nullptr;
+    void* v_slab = nullptr;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    unsigned int* tickets = nullptr;
+    size_t ticket_cells = 0;
+    float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_out = nullptr;
+    size_t stage_rows = 0;
+    void* gather_buf = nullptr;
+    size_t gather_bytes = 0;
+    std::vector<SlotState> slots;
+    mutable std::string err;
+    itk_stats stats{};
+    int sm_count = 148;
+    int forced_splits = 0;
+    // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<int> prof_tags;
+    size_t prof_used = 0;
+
+    int fail(int code, std::string msg) const {
+        err = std::move(msg);
+        return code;
+    }
+    int cuda_fail(cudaError_t e, const char* what) const {
+        return fail(ITK_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    size_t row_len() const { return static_cast<size_t>(cfg.kv_heads) * cfg.head_dim; }
+    size_t q_width() const { return static_cast<size_t>(cfg.q_heads) * cfg.head_dim; }
+    uint64_t stored(uint32_t layer, uint64_t appended) const {
+        return window[layer] ? (appended < window[layer] ? appended : window[layer]) : appended;
+    }
+    void* layer_ptr(void* slab, uint32_t layer) const {
+        return static_cast<unsigned char*>(slab) + layer_off[layer] * elem_bytes;
+    }
+};
+
+namespace {
+
+#define ITK_CUDA(b, call, what)                                \
+    do {                                                       \
+        cudaError_t e_ = (call);                               \
+        if (e_ != cudaSuccess) return (b)->cuda_fail(e_, what); \
+    } while (0)
+
+int check_slot(const itk_backend* b, uint32_t slot) {
+    if (slot >= b->cfg.n_slots)
+        return b->fail(ITK_ERR_INVALID_SLOT, "slot " + zu(slot) + " out of range, backend has " + zu(b->cfg.n_slots) + " slots");
+    return ITK_OK;
+}
+int check_layer(const itk_backend* b, uint32_t layer) {
+    if (layer >= b->cfg.n_layers)
+        return b->fail(ITK_ERR_INVALID_LAYER,
+                       "layer " + zu(layer) + " out of range, cache has " + zu(b->cfg.n_layers) + " layers");
+    return ITK_OK;
+}
+
+// KV splits for a decode launch: minimise waves x (tiles per CTA + fixed cost)
+// over the CTA slots the device offers (2 resident CTAs per SM).
+uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uint32_t tile) {
+    if (b->forced_splits > 0) {
+        uint64_t s = static_cast<uint64_t>(b->forced_splits);
+        const uint64_t by_len = (n_max + tile - 1) / tile;
+        if (s > by_len) s = by_len;
+        if (s * cells > kPartCellSplits) s = kPartCellSplits / cells;
+        return static_cast<uint32_t>(s < 1 ? 1 : s);
+    }
+    const uint64_t slots = static_cast<uint64_t>(b->sm_count) * 2;
+    uint64_t max_s = (n_max + 4 * tile - 1) / (4 * tile);  // at least four tiles per CTA
+    if (max_s < 1) max_s = 1;
+    if (max_s > 256) max_s = 256;
+    if (cells == 0) return 1;
+    if (max_s * cells > kPartCellSplits) max_s = kPartCellSplits / cells;
+    if (max_s < 1) max_s = 1;
+    uint64_t best = 1;
+    double best_cost = 1e300;
+    for (uint64_t s = 1; s <= max_s; ++s) {
+        const uint64_t ctas = cells * s;
+        const uint64_t waves = (ctas + slots - 1) / slots;
+        const uint64_t per = (n_max + s - 1) / s;
+        const uint64_t tiles = (per + tile - 1) / tile;
+        const double cost = static_cast<double>(waves) * (static_cast<double>(tiles) + 3.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = s;
+        }
+    }
+    return static_cast<uint32_t>(best);
+}
+
+// Event pair around one kernel launch while profiling is on; returns the pair's index or -1.
+long prof_begin(itk_backend* b, int tag) {
+    if (b->prof_used + 2 > b->prof_events.size()) return -1;
+    const long at = static_cast<long>(b->prof_used);
+    b->prof_used += 2;
+    b->prof_tags[at / 2] = tag;
+    cudaEventRecord(b->prof_events[at], b->stream);
+    return at;
+}
+void prof_end(itk_backend* b, long at) {
+    if (at >= 0) cudaEventRecord(b->prof_events[at + 1], b->stream);
+}
+
+void fill_layer_view(const itk_backend* b, uint32_t layer, itk::LayerView* v) {
+    v->k = b->layer_ptr(b->k_slab, layer);
+    v->v = b->layer_ptr(b->v_slab, layer);
+    v->ring = b->ring[layer];
+    v->window = b->window[layer];
+    v->kv_heads = b->cfg.kv_heads;
+    v->head_dim = b->cfg.head_dim;
+}
+
+// Launch the append kernel for `n` sequences (device sources).
+int run_append(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, uint32_t rows, const float* d_k,
+               const float* d_v) {
+    for (uint32_t at = 0; at < n; at += itk::kMaxSeqsPerLaunch) {
+        const uint32_t m = (n - at < static_cast<uint32_t>(itk::kMaxSeqsPerLaunch)) ? n - at : itk::kMaxSeqsPerLaunch;
+        AppendLaunch p{};
+        p.k = b->layer_ptr(b->k_slab, layer);
+        p.v = b->layer_ptr(b->v_slab, layer);
+        p.k_src = d_k + static_cast<size_t>(at) * rows * b->row_len();
+        p.v_src = d_v + static_cast<size_t>(at) * rows * b->row_len();
+        p.ring = b->ring[layer];
+        p.kv_heads = b->cfg.kv_heads;
+        p.head_dim = b->cfg.head_dim;
+        p.rows = rows;
+        p.n_seqs = m;
+        for (uint32_t i = 0; i < m; ++i) p.seq[i] = seqs[at + i];
+        const long ev = prof_begin(b, 1);
+        ITK_CUDA(b, itk::launch_append(p, b->f16, b->stream, &b->stats.kernel_launches), "append launch");
+        prof_end(b, ev);
+    }
+    return ITK_OK;
+}
+
+// Launch attention for `n` sequences of `rows` rows each (device q / out).
+int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, uint32_t rows, const float* d_q,
+                  float* d_out) {
+    const uint32_t D = b->cfg.head_dim;
+    const uint32_t HY = b->cfg.kv_heads * b->gchunks;
+    const bool decode = b->f16 && itk::decode_f16_supported(D, rows);
+    // grid.z carries n_seqs * rows and is limited to 65535
+    uint32_t per_launch = itk::kMaxSeqsPerLaunch;
+    while (per_launch > 1 && static_cast<uint64_t>(per_launch) * rows > 65535) per_launch >>= 1;
+    if (static_cast<uint64_t>(rows) > 65535)
+        return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(rows) + " rows exceed one launch's 65535-row limit");
+    for (uint32_t at = 0; at < n; at += per_launch) {
+        const uint32_t m = (n - at < per_launch) ? n - at : per_launch;
+        AttnLaunch p{};
+        fill_layer_view(b, layer, &p.layer);
+        p.q = d_q + static_cast<size_t>(at) * rows * b->q_width();
+        p.out = d_out + static_cast<size_t>(at) * rows * b->q_width();
+        p.part_o = b->part_o;
+        p.part_ml = b->part_ml;
+        p.tickets = b->tickets;
+        p.q_heads = b->cfg.q_heads;
+        p.group = b->group;
+        p.gchunks = b->gchunks;
+        p.rows = rows;
+        p.n_seqs = m;
+        p.scale = 1.0f / sqrtf(static_cast<float>(D));
+        uint64_t n_max = 0, keys = 0;
+        for (uint32_t i = 0; i < m; ++i) {
+            p.seq[i] = seqs[at + i];
+            const uint64_t span = p.seq[i].kv_hi - p.seq[i].kv_lo;
+            if (span > n_max) n_max = span;
+            keys += span;  // upper bound for multi-row launches; exact for decode
+        }
+        const uint64_t cells = static_cast<uint64_t>(m) * rows * HY;
+        if (cells > b->ticket_cells)
+            return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(cells) + " (row, head) cells exceed the scratch of " +
+                                                 zu(b->ticket_cells));
+        p.splits = choose_splits(b, cells, n_max, decode ? 64 : 128);
+        b->stats.last_splits = p.splits;
+        b->stats.kv_bytes_read += keys * b->cfg.kv_heads * D * 2ull * b->elem_bytes;
+        const long ev = prof_begin(b, 0);
+        if (decode)
+            ITK_CUDA(b, itk::launch_decode_f16(p, b->stream, &b->stats.kernel_launches), "decode attention launch");
+        else
+            ITK_CUDA(b, itk::launch_attn_general(p, b->f16, b->stream, &b->stats.kernel_launches),
+                     "attention launch");
+        prof_end(b, ev);
+    }
+    return ITK_OK;
+}
+
+// Shared validation of one attention step; fills `seqs`.  Mirrors
+// crates/cpu-compute/src/cpu.rs:558-581 (position cross-check) and
+// crates/attention/src/cache.rs:445-471 (checkpoint range) before anything moves.
+int validate_step(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots, const uint64_t* positions,
+                  uint32_t rows, std::vector<SeqDesc>* seqs) {
+    if (int rc = check_layer(b, layer)) return rc;
+    if (n_seqs == 0 || rows == 0) return b->fail(ITK_ERR_INVALID_ARGUMENT, "attention: zero sequences or zero rows");
+    if (rows > b->cfg.chunk_cap)
+        return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(rows) + " rows exceed the backend's chunk cap of " +
+                                             zu(b->cfg.chunk_cap) + "; forward in chunks");
+    if (n_seqs > b->cfg.n_slots)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "attention: more sequences than slots");
+    seqs->resize(n_seqs);
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        if (int rc = check_slot(b, slots[i])) return rc;
+        for (uint32_t j = 0; j < i; ++j)
+            if (slots[j] == slots[i])
+                return b->fail(ITK_ERR_INVALID_ARGUMENT, "attention: slot " + zu(slots[i]) + " listed twice");
+        const SlotState& st = b->slots[slots[i]];
+        const uint64_t appended = st.appended[layer];
+        const uint64_t start = positions[i];
+        if (appended != start)
+            return b->fail(ITK_ERR_STEP_FAILED,
+                           "attention: KV state for layer " + zu(layer) + " is at position " + zu(appended) +
+                               " but the sequence cache is at position " + zu(start) +
+                               ": the two disagree, so attending would read the wrong history. Pair one Cache with "
+                               "one slot per sequence, or call itk_reset when a sequence is abandoned");
+        if (st.live) {
+            const uint64_t limit = st.bases[layer] + st.max_round;
+            if (start + rows > limit) {
+                const uint64_t bad = start > limit ? start : limit;
+                return b->fail(ITK_ERR_CHECKPOINT_RANGE_EXCEEDED,
+                               "attention: layer " + zu(layer) + " append at position " + zu(bad) +
+                                   " is outside the live checkpoint's saved range (first unsaved position " + zu(limit) +
+                                   "); refusing so a later rewind cannot meet a slot it cannot restore");
+            }
+        }
+        if (b->window[layer] == 0 && start + rows > b->ring[layer])
+            return b->fail(ITK_ERR_CAPACITY, "attention: position " + zu(start + rows) + " is past the slot's context "
+                                             "capacity of " + zu(b->ring[layer]) + " positions");
+        if (start + rows > 0xfffffff0ull) return b->fail(ITK_ERR_CAPACITY, "attention: position exceeds 32 bits");
+        SeqDesc d;
+        d.slot = slots[i];
+        d.q_pos0 = static_cast<uint32_t>(start);
+        d.kv_hi = static_cast<uint32_t>(start + rows);
+        d.kv_lo = 0;
+        if (b->window[layer] && start + 1 > b->window[layer]) d.kv_lo = static_cast<uint32_t>(start + 1 - b->window[layer]);
+        (*seqs)[i] = d;
+    }
+    return ITK_OK;
+}
+
+int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots, const uint64_t* positions,
+                uint32_t rows, const float* d_q, const float* d_k, const float* d_v, float* d_out) {
+    std::vector<SeqDesc> seqs;
+    if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
+    if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        SlotState& st = b->slots[slots[i]];
+        st.appended[layer] += rows;
+        st.built = true;
+    }
+    b->stats.rows_appended += static_cast<uint64_t>(n_seqs) * rows;
+    b->stats.attention_calls += 1;
+    return run_attention(b, layer, n_seqs, seqs.data(), rows, d_q, d_out);
+}
+
+int ensure_gather(itk_backend* b, size_t bytes) {
+    if (bytes <= b->gather_bytes) return ITK_OK;
+    if (b->gather_buf) cudaFree(b->gather_buf);
+    b->gather_buf = nullptr;
+    b->gather_bytes = 0;
+    ITK_CUDA(b, cudaMalloc(&b->gather_buf, bytes), "gather buffer allocation");
+    b->gather_bytes = bytes;
+    return ITK_OK;
+}
+
+// Gather or scatter layers [l0, l1) of one slot between the slabs and `snap_base`.
+int run_copy(itk_backend* b, uint32_t slot, void* snap_base, const std::vector<uint32_t>& layers,
+             const std::vector<uint64_t>& first, const std::vector<uint64_t>& rows, const std::vector<uint64_t>& k_off,
+             const std::vector<uint64_t>& v_off, bool to_snapshot) {
+    const uint32_t row_bytes = b->cfg.head_dim * b->elem_bytes;
+    const uint32_t vb = (row_bytes % 16 == 0) ? 16 : b->elem_bytes;
+    const uint64_t units_per_row = static_cast<uint64_t>(b->cfg.kv_heads) * (row_bytes / vb);
+    for (size_t at = 0; at < layers.size(); at += itk::kMaxLayersPerLaunch) {
+        const size_t m = (layers.size() - at < static_cast<size_t>(itk::kMaxLayersPerLaunch)) ? layers.size() - at
+                                                                                               : itk::kMaxLayersPerLaunch;
+        CopyLaunch p{};
+        p.k_slab = b->k_slab;
+        p.v_slab = b->v_slab;
+        p.snap = snap_base;
+        p.slot = slot;
+        p.kv_heads = b->cfg.kv_heads;
+        p.head_dim = b->cfg.head_dim;
+        p.n_layers = static_cast<uint32_t>(m);
+        p.elem_bytes = b->elem_bytes;
+        p.to_snapshot = to_snapshot ? 1 : 0;
+        p.vec_prefix[0] = 0;
+        for (size_t i = 0; i < m; ++i) {
+            const uint32_t l = layers[at + i];
+            p.layer[i].slab_off = b->layer_off[l];
+            p.layer[i].snap_k = k_off[at + i];
+            p.layer[i].snap_v = v_off[at + i];
+            p.layer[i].ring = b->ring[l];
+            p.layer[i].first_pos = static_cast<uint32_t>(first[at + i]);
+            p.layer[i].rows = static_cast<uint32_t>(rows[at + i]);
+            p.vec_prefix[i + 1] = p.vec_prefix[i] + rows[at + i] * units_per_row;
+        }
+        p.total_vec = 2 * p.vec_prefix[m];
+        ITK_CUDA(b, itk::launch_snapshot_copy(p, b->stream, &b->stats.kernel_launches), "snapshot copy launch");
+    }
+    return ITK_OK;
+}
+
+void drop_slot(itk_backend* b, uint32_t slot) {
+    SlotState& st = b->slots[slot];
+    st.id = g_next_cache_id.fetch_add(1);
+    st.built = false;
+    st.appended.assign(b->cfg.n_layers, 0);
+    st.live = false;
+    st.next_serial = 0;
+    st.bases.clear();
+}
+
+// crates/attention/src/cache.rs:719-728
+int check_live(const itk_backend* b, const SlotState& st, const itk_checkpoint* cp) {
+    if (st.live && st.live_serial == cp->serial && cp->id == st.id) return ITK_OK;
+    return b->fail(ITK_ERR_STALE_CHECKPOINT, "checkpoint " + zu(cp->serial) +
+                                                 " is not this cache's live checkpoint (already released or foreign)");
+}
+
+}  // namespace
+
+extern "C" {
+
+int itk_backend_create(const itk_config* cfg, itk_backend** out) {
+    auto refuse = [](int code, std::string msg) {
+        g_create_error = std::move(msg);
+        return code;
+    };
+    if (!cfg || !out) return refuse(ITK_ERR_INVALID_ARGUMENT, "null config or output pointer");
+    if (cfg->n_layers == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "layer pattern must be positive, got 0");
+    if (cfg->kv_heads == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "num_kv_heads must be positive, got 0");
+    if (cfg->head_dim == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "head_dim must be positive, got 0");
+    if (cfg->q_heads == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "num_q_heads must be positive, got 0");
+    if (cfg->q_heads % cfg->kv_heads != 0)
+        return refuse(ITK_ERR_NON_DIVISIBLE_HEADS, zu(cfg->q_heads) + " query heads do not divide evenly across " +
+                                                       zu(cfg->kv_heads) + " KV heads");
+    if (cfg->n_slots == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "n_slots must be positive, got 0");
+    if (cfg->max_context == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "max_context must be positive, got 0");
+    if (cfg->chunk_cap == 0) return refuse(ITK_ERR_ZERO_DIMENSION, "chunk_cap must be positive, got 0");
+    if (cfg->kv_dtype != ITK_KV_F32 && cfg->kv_dtype != ITK_KV_F16)
+        return refuse(ITK_ERR_INVALID_ARGUMENT, "kv_dtype must be ITK_KV_F32 or ITK_KV_F16");
+    if (cfg->head_dim > 256) return refuse(ITK_ERR_CAPACITY, "head_dim above 256 is not supported");
+
+    itk_backend* b = new (std::nothrow) itk_backend();
+    if (!b) return refuse(ITK_ERR_CUDA, "out of host memory");
+    b->cfg = *cfg;
+    b->cfg.layer_window = nullptr;
+    b->f16 = cfg->kv_dtype == ITK_KV_F16;
+    b->elem_bytes = b->f16 ? 2 : 4;
+    b->group = cfg->q_heads / cfg->kv_heads;
+    b->gchunks = (b->group + itk::kHeadsPerCta - 1) / itk::kHeadsPerCta;
+    const uint64_t row = static_cast<uint64_t>(cfg->kv_heads) * cfg->head_dim;
+    uint64_t total = 0;
+    for (uint32_t l = 0; l < cfg->n_layers; ++l) {
+        const uint32_t w = cfg->layer_window ? cfg->layer_window[l] : 0;
+        uint64_t ring = w ? static_cast<uint64_t>(w) + cfg->chunk_cap : cfg->max_context;
+        if (ring > 0xfffffff0ull) {
+            delete b;
+            return refuse(ITK_ERR_SIZE_OVERFLOW, "windowed layer storage: element count overflows");
+        }
+        b->window.push_back(w);
+        b->ring.push_back(static_cast<uint32_t>(ring));
+        b->layer_off.push_back(total);
+        uint64_t layer_elems;
+        if (__builtin_mul_overflow(ring * cfg->n_slots, row, &layer_elems) ||
+            __builtin_add_overflow(total, layer_elems, &total) || total > (1ull << 46)) {
+            delete b;
+            return refuse(ITK_ERR_SIZE_OVERFLOW, "kv storage: element count overflows");
+        }
+    }
+    b->slab_elems = total;
+
+    auto cuda_refuse = [&](cudaError_t e, const char* what) {
+        std::string msg = std::string(what) + ": " + cudaGetErrorString(e);
+        itk_backend_destroy(b);
+        return refuse(ITK_ERR_CUDA, msg);
+    };
+    cudaError_t e = cudaSetDevice(cfg->device);
+    if (e != cudaSuccess) return cuda_refuse(e, "cudaSetDevice");
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, cfg->device);
+    if (e != cudaSuccess) return cuda_refuse(e, "cudaGetDeviceProperties");
+    if (prop.major != 10)
+        return cuda_refuse(cudaErrorNoKernelImageForDevice, "this library carries sm_100a kernels only");
+    b->sm_count = prop.multiProcessorCount;
+    e = itk::configure_decode_f16();
+    if (e != cudaSuccess) return cuda_refuse(e, "kernel attribute setup");
+    e = cudaStreamCreateWithFlags(&b->own_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return cuda_refuse(e, "cudaStreamCreate");
+    b->stream = b->own_stream;
+    e = cudaMalloc(&b->k_slab, total * b->elem_bytes);
+    if (e != cudaSuccess) return cuda_refuse(e, "K slab allocation");
+    e = cudaMalloc(&b->v_slab, total * b->elem_bytes);
+    if (e != cudaSuccess) return cuda_refuse(e, "V slab allocation");
+    // Windowed rings start zero-filled like the reference's (cache.rs:139); global rows are written before read.
+    for (uint32_t l = 0; l < cfg->n_layers; ++l)
+        if (b->window[l]) {
+            const size_t bytes = static_cast<size_t>(b->ring[l]) * cfg->n_slots * row * b->elem_bytes;
+            cudaMemsetAsync(b->layer_ptr(b->k_slab, l), 0, bytes, b->stream);
+            cudaMemsetAsync(b->layer_ptr(b->v_slab, l), 0, bytes, b->stream);
+        }
+    const uint32_t HY = cfg->kv_heads * b->gchunks;
+    b->ticket_cells = static_cast<size_t>(cfg->n_slots) * cfg->chunk_cap * HY;
+    if (b->ticket_cells < 64u * HY) b->ticket_cells = 64u * HY;
+    e = cudaMalloc(&b->tickets, b->ticket_cells * sizeof(unsigned int));
+    if (e != cudaSuccess) return cuda_refuse(e, "ticket allocation");
+    cudaMemsetAsync(b->tickets, 0, b->ticket_cells * sizeof(unsigned int), b->stream);
+    e = cudaMalloc(&b->part_o, kPartCellSplits * itk::kHeadsPerCta * cfg->head_dim * sizeof(float));
+    if (e != cudaSuccess) return cuda_refuse(e, "partial-output scratch allocation");
+    e = cudaMalloc(&b->part_ml, kPartCellSplits * itk::kHeadsPerCta * 2 * sizeof(float));
+    if (e != cudaSuccess) return cuda_refuse(e, "partial-stat scratch allocation");
+    b->stage_rows = static_cast<size_t>(cfg->n_slots) * cfg->chunk_cap;
+    if (b->stage_rows < 64) b->stage_rows = 64;
+    e = cudaMalloc(&b->d_q, b->stage_rows * b->q_width() * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&b->d_out, b->stage_rows * b->q_width() * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&b->d_k, b->stage_rows * b->row_len() * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&b->d_v, b->stage_rows * b->row_len() * sizeof(float));
+    if (e != cudaSuccess) return cuda_refuse(e, "staging allocation");
+    e = cudaStreamSynchronize(b->stream);
+    if (e != cudaSuccess) return cuda_refuse(e, "initialisation");
+    b->slots.resize(cfg->n_slots);
+    for (uint32_t s = 0; s < cfg->n_slots; ++s) drop_slot(b, s);
+    if (const char* env = std::getenv("ITK_DECODE_SPLITS")) b->forced_splits = std::atoi(env);
+    *out = b;
+    return ITK_OK;
+}
+
+void itk_backend_destroy(itk_backend* b) {
+    if (!b) return;
+    cudaSetDevice(b->cfg.device);
+    if (b->stream) cudaStreamSynchronize(b->stream);
+    cudaFree(b->k_slab);
+    cudaFree(b->v_slab);
+    cudaFree(b->tickets);
+    cudaFree(b->part_o);
+    cudaFree(b->part_ml);
+    cudaFree(b->d_q);
+    cudaFree(b->d_k);
+    cudaFree(b->d_v);
+    cudaFree(b->d_out);
+    cudaFree(b->gather_buf);
+    for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
+    if (b->own_stream) cudaStreamDestroy(b->own_stream);
+    delete b;
+}
+
+const char* itk_last_error(const itk_backend* b) { return b ? b->err.c_str() : g_create_error.c_str(); }
+
+int itk_set_stream(itk_backend* b, void* cuda_stream) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    b->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : b->own_stream;
+    return ITK_OK;
+}
+
+int itk_synchronize(itk_backend* b) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "synchronize");
+    return ITK_OK;
+}
+
+int itk_get_stats(const itk_backend* b, itk_stats* out) {
+    if (!b || !out) return ITK_ERR_INVALID_ARGUMENT;
+    *out = b->stats;
+    return ITK_OK;
+}
+
+int itk_profile_enable(itk_backend* b, uint32_t capacity) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
+    b->prof_events.clear();
+    b->prof_tags.assign(capacity, 0);
+    b->prof_used = 0;
+    for (uint32_t i = 0; i < 2 * capacity; ++i) {
+        cudaEvent_t e;
+        ITK_CUDA(b, cudaEventCreate(&e), "profile event creation");
+        b->prof_events.push_back(e);
+    }
+    return ITK_OK;
+}
+
+int itk_profile_read(itk_backend* b, double* attention_ms, uint64_t* attention_launches, double* append_ms,
+                     uint64_t* append_launches) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "profile read");
+    double ms[2] = {0.0, 0.0};
+    uint64_t n[2] = {0, 0};
+    for (size_t at = 0; at + 1 < b->prof_used; at += 2) {
+        float t = 0.f;
+        ITK_CUDA(b, cudaEventElapsedTime(&t, b->prof_events[at], b->prof_events[at + 1]), "profile read");
+        const int tag = b->prof_tags[at / 2];
+        ms[tag] += t;
+        n[tag] += 1;
+    }
+    if (attention_ms) *attention_ms = ms[0];
+    if (attention_launches) *attention_launches = n[0];
+    if (append_ms) *append_ms = ms[1];
+    if (append_launches) *append_launches = n[1];
+    b->prof_used = 0;
+    return ITK_OK;
+}
+
+int itk_attention_batch_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                               const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
+                               const float* d_v, float* d_out) {
+    if (!b || !slots || !positions || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    return step_device(b, layer, n_seqs, slots, positions, rows, d_q, d_k, d_v, d_out);
+}
+
+int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                        const uint64_t* positions, uint32_t rows, const float* q, const float* k, const float* v,
+                        float* out) {
+    if (!b || !slots || !positions || !q || !k || !v || !out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    std::vector<SeqDesc> seqs;
+    if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
+    const size_t total_rows = static_cast<size_t>(n_seqs) * rows;
+    if (total_rows > b->stage_rows)
+        return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(total_rows) + " rows exceed the staging capacity of " +
+                                             zu(b->stage_rows));
+    const size_t qb = total_rows * b->q_width() * sizeof(float), kb = total_rows * b->row_len() * sizeof(float);
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_k, k, kb, cudaMemcpyHostToDevice, b->stream), "k upload");
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_v, v, kb, cudaMemcpyHostToDevice, b->stream), "v upload");
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_q, q, qb, cudaMemcpyHostToDevice, b->stream), "q upload");
+    if (int rc = step_device(b, layer, n_seqs, slots, positions, rows, b->d_q, b->d_k, b->d_v, b->d_out)) return rc;
+    ITK_CUDA(b, cudaMemcpyAsync(out, b->d_out, qb, cudaMemcpyDeviceToHost, b->stream), "output download");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention");
+    return ITK_OK;
+}
+
+int itk_attention(itk_backend* b, uint32_t slot, uint32_t layer, const float* q, size_t q_len, const float* k,
+                  size_t k_len, const float* v, size_t v_len, uint64_t position, float* out) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    // crates/cpu-compute/src/cpu.rs:532-556: whole q rows, then k/v lengths for that row count.
+    const size_t qw = b->q_width(), kw = b->row_len();
+    if (q_len % qw != 0)
+        return b->fail(ITK_ERR_STEP_FAILED, "attention: query projection holds " + zu(q_len) +
+                                                " elements, not a whole number of " + zu(qw) + "-wide rows");
+    const size_t rows = q_len / qw;
+    if (k_len != rows * kw || v_len != rows * kw)
+        return b->fail(ITK_ERR_STEP_FAILED, "attention: key/value projections hold " + zu(k_len) + "/" + zu(v_len) +
+                                                " elements for " + zu(rows) + " rows, expected " + zu(rows * kw) + "/" +
+                                                zu(rows * kw));
+    if (rows == 0) return ITK_OK;
+    return itk_attention_batch(b, layer, 1, &slot, &position, static_cast<uint32_t>(rows), q, k, v, out);
+}
+
+int itk_gqa_attention(itk_backend* b, uint32_t slot, uint32_t layer, const float* q, size_t q_len, uint32_t rows,
+                      const uint64_t* query_positions, float* out) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    if (int rc = check_layer(b, layer)) return rc;
+    const size_t expected = static_cast<size_t>(rows) * b->q_width();
+    if (q_len != expected) return b->fail(ITK_ERR_SHAPE_MISMATCH, "q: got " + zu(q_len) + ", expected " + zu(expected));
+    if (rows == 0) return ITK_OK;
+    if (!q || !query_positions || !out) return ITK_ERR_INVALID_ARGUMENT;
+    const SlotState& st = b->slots[slot];
+    const uint64_t appended = st.appended[layer];
+    const uint64_t first_visible = appended - b->stored(layer, appended);
+    // Each query row becomes its own one-row unit so that positions need not be consecutive.
+    std::vector<SeqDesc> seqs(rows);
+    for (uint32_t r = 0; r < rows; ++r) {
+        const uint64_t p = query_positions[r];
+        uint64_t lo = first_visible;
+        if (b->window[layer] && p + 1 > b->window[layer] && p + 1 - b->window[layer] > lo) lo = p + 1 - b->window[layer];
+        const uint64_t hi = (p + 1 < appended) ? p + 1 : appended;
+        if (hi <= lo) return b->fail(ITK_ERR_NO_VISIBLE_KEYS, "query at position " + zu(p) + " has no visible keys");
+        seqs[r].slot = slot;
+        seqs[r].q_pos0 = static_cast<uint32_t>(hi - 1);  // the row sees [lo, hi); its own position caps hi
+        seqs[r].kv_lo = static_cast<uint32_t>(lo);
+        seqs[r].kv_hi = static_cast<uint32_t>(hi);
+    }
+    for (uint32_t at = 0; at < rows; at += static_cast<uint32_t>(b->stage_rows)) {
+        const uint32_t m = (rows - at < b->stage_rows) ? rows - at : static_cast<uint32_t>(b->stage_rows);
+        const size_t bytes = static_cast<size_t>(m) * b->q_width() * sizeof(float);
+        ITK_CUDA(b, cudaMemcpyAsync(b->d_q, q + static_cast<size_t>(at) * b->q_width(), bytes, cudaMemcpyHostToDevice,
+                                    b->stream), "q upload");
+        if (int rc = run_attention(b, layer, m, seqs.data() + at, 1, b->d_q, b->d_out)) return rc;
+        ITK_CUDA(b, cudaMemcpyAsync(out + static_cast<size_t>(at) * b->q_width(), b->d_out, bytes,
+                                    cudaMemcpyDeviceToHost, b->stream), "output download");
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention");
+    }
+    b->stats.attention_calls += 1;
+    return ITK_OK;
+}
+
+int itk_append_rows(itk_backend* b, uint32_t slot, uint32_t layer, const float* k, const float* v, uint32_t rows,
+                    uint64_t start) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    SlotState& st = b->slots[slot];
+    // crates/attention/src/cache.rs:445-471: checkpoint range, then layer, then order.
+    if (st.live && layer < st.bases.size()) {
+        const uint64_t limit = st.bases[layer] + st.max_round;
+        if (start + rows > limit && rows > 0) {
+            const uint64_t bad = start > limit ? start : limit;
+            return b->fail(ITK_ERR_CHECKPOINT_RANGE_EXCEEDED,
+                           "layer " + zu(layer) + " append at position " + zu(bad) +
+                               " is outside the live checkpoint's saved range (first unsaved position " + zu(limit) +
+                               "); refusing so a later rewind cannot meet a slot it cannot restore");
+        }
+    }
+    if (int rc = check_layer(b, layer)) return rc;
+    if (start != st.appended[layer])
+        return b->fail(ITK_ERR_OUT_OF_ORDER_POSITION, "layer " + zu(layer) + " appends must be in order: expected position " +
+                                                          zu(st.appended[layer]) + ", got " + zu(start));
+    if (rows == 0) return ITK_OK;
+    if (!k || !v) return ITK_ERR_INVALID_ARGUMENT;
+    if (b->window[layer] == 0 && start + rows > b->ring[layer])
+        return b->fail(ITK_ERR_CAPACITY, "append: position " + zu(start + rows) + " is past the slot's context capacity of " +
+                                             zu(b->ring[layer]) + " positions");
+    if (b->window[layer] != 0 && rows > b->ring[layer])
+        return b->fail(ITK_ERR_CAPACITY, "append: " + zu(rows) + " rows exceed the ring of " + zu(b->ring[layer]));
+    for (uint32_t at = 0; at < rows; at += static_cast<uint32_t>(b->stage_rows)) {
+        const uint32_t m = (rows - at < b->stage_rows) ? rows - at : static_cast<uint32_t>(b->stage_rows);
+        const size_t bytes = static_cast<size_t>(m) * b->row_len() * sizeof(float);
+        ITK_CUDA(b, cudaMemcpyAsync(b->d_k, k + static_cast<size_t>(at) * b->row_len(), bytes, cudaMemcpyHostToDevice,
+                                    b->stream), "k upload");
+        ITK_CUDA(b, cudaMemcpyAsync(b->d_v, v + static_cast<size_t>(at) * b->row_len(), bytes, cudaMemcpyHostToDevice,
+                                    b->stream), "v upload");
+        SeqDesc d{slot, static_cast<uint32_t>(start + at), 0, static_cast<uint32_t>(start + at + m)};
+        if (int rc = run_append(b, layer, 1, &d, m, b->d_k, b->d_v)) return rc;
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "append");
+    }
+    st.appended[layer] += rows;
+    st.built = true;
+    b->stats.rows_appended += rows;
+    return ITK_OK;
+}
+
+int itk_append_rows_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                           const uint64_t* starts, uint32_t rows, const float* d_k, const float* d_v) {
+    if (!b || !slots || !starts || !d_k || !d_v) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_layer(b, layer)) return rc;
+    if (n_seqs == 0 || rows == 0) return ITK_OK;
+    std::vector<SeqDesc> seqs(n_seqs);
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        if (int rc = check_slot(b, slots[i])) return rc;
+        for (uint32_t j = 0; j < i; ++j)
+            if (slots[j] == slots[i])
+                return b->fail(ITK_ERR_INVALID_ARGUMENT, "append: slot " + zu(slots[i]) + " listed twice");
+        const SlotState& st = b->slots[slots[i]];
+        if (st.live) {
+            const uint64_t limit = st.bases[layer] + st.max_round;
+            if (starts[i] + rows > limit) {
+                const uint64_t bad = starts[i] > limit ? starts[i] : limit;
+                return b->fail(ITK_ERR_CHECKPOINT_RANGE_EXCEEDED,
+                               "layer " + zu(layer) + " append at position " + zu(bad) +
+                                   " is outside the live checkpoint's saved range (first unsaved position " + zu(limit) +
+                                   "); refusing so a later rewind cannot meet a slot it cannot restore");
+            }
+        }
+        if (starts[i] != st.appended[layer])
+            return b->fail(ITK_ERR_OUT_OF_ORDER_POSITION, "layer " + zu(layer) + " appends must be in order: expected position " +
+                                                              zu(st.appended[layer]) + ", got " + zu(starts[i]));
+        if (b->window[layer] == 0 && starts[i] + rows > b->ring[layer])
+            return b->fail(ITK_ERR_CAPACITY, "append: position " + zu(starts[i] + rows) +
+                                                 " is past the slot's context capacity of " + zu(b->ring[layer]) + " positions");
+        if (b->window[layer] != 0 && rows > b->ring[layer])
+            return b->fail(ITK_ERR_CAPACITY, "append: " + zu(rows) + " rows exceed the ring of " + zu(b->ring[layer]));
+        if (starts[i] + rows > 0xfffffff0ull) return b->fail(ITK_ERR_CAPACITY, "append: position exceeds 32 bits");
+        seqs[i] = SeqDesc{slots[i], static_cast<uint32_t>(starts[i]), 0, static_cast<uint32_t>(starts[i] + rows)};
+    }
+    if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        b->slots[slots[i]].appended[layer] += rows;
+        b->slots[slots[i]].built = true;
+    }
+    b->stats.rows_appended += static_cast<uint64_t>(n_seqs) * rows;
+    return ITK_OK;
+}
+
+int itk_append(itk_backend* b, uint32_t slot, uint32_t layer, const float* k, size_t k_len, const float* v,
+               size_t v_len, uint64_t position) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    const size_t row = b->row_len();
+    if (k_len != row) return b->fail(ITK_ERR_SHAPE_MISMATCH, "k: got " + zu(k_len) + ", expected " + zu(row));
+    if (v_len != row) return b->fail(ITK_ERR_SHAPE_MISMATCH, "v: got " + zu(v_len) + ", expected " + zu(row));
+    return itk_append_rows(b, slot, layer, k, v, 1, position);
+}
+
+int itk_next_position(const itk_backend* b, uint32_t slot, uint32_t layer, uint64_t* out) {
+    if (!b || !out) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_slot(b, slot)) return rc;
+    if (int rc = check_layer(b, layer)) return rc;
+    *out = b->slots[slot].appended[layer];
+    return ITK_OK;
+}
+
+int itk_stored_len(const itk_backend* b, uint32_t slot, uint32_t layer, uint64_t* out) {
+    if (!b || !out) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_slot(b, slot)) return rc;
+    if (int rc = check_layer(b, layer)) return rc;
+    *out = b->stored(layer, b->slots[slot].appended[layer]);
+    return ITK_OK;
+}
+
+int itk_view_gather(itk_backend* b, uint32_t slot, uint32_t layer, void* keys, void* values, uint64_t* first_position,
+                    uint64_t* rows) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    if (int rc = check_layer(b, layer)) return rc;
+    const uint64_t appended = b->slots[slot].appended[layer];
+    const uint64_t n = b->stored(layer, appended);
+    if (first_position) *first_position = appended - n;
+    if (rows) *rows = n;
+    if (n == 0 || (!keys && !values)) return ITK_OK;
+    const uint64_t block = n * b->row_len();
+    if (int rc = ensure_gather(b, 2 * block * b->elem_bytes)) return rc;
+    if (int rc = run_copy(b, slot, b->gather_buf, {layer}, {appended - n}, {n}, {0}, {block}, true)) return rc;
+    unsigned char* base = static_cast<unsigned char*>(b->gather_buf);
+    if (keys)
+        ITK_CUDA(b, cudaMemcpyAsync(keys, base, block * b->elem_bytes, cudaMemcpyDeviceToHost, b->stream), "view download");
+    if (values)
+        ITK_CUDA(b, cudaMemcpyAsync(values, base + block * b->elem_bytes, block * b->elem_bytes, cudaMemcpyDeviceToHost,
+                                    b->stream), "view download");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "view gather");
+    return ITK_OK;
+}
+
+int itk_restore_bulk(itk_backend* b, uint32_t slot, uint32_t layer, uint64_t first_position, const float* keys,
+                     size_t keys_len, const float* values, size_t values_len) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    // crates/attention/src/cache.rs:520-557, same order.
+    const size_t row = b->row_len();
+    if (keys_len != values_len || keys_len % row != 0)
+        return b->fail(ITK_ERR_SHAPE_MISMATCH, "bulk restore rows: got " + zu(keys_len) + ", expected " + zu(values_len));
+    const uint64_t rows = keys_len / row;
+    if (int rc = check_layer(b, layer)) return rc;
+    SlotState& st = b->slots[slot];
+    if (st.appended[layer] != 0)
+        return b->fail(ITK_ERR_BULK_RESTORE_NOT_FRESH, "layer " + zu(layer) + " already holds " + zu(st.appended[layer]) +
+                                                           " appended positions; bulk restore installs into a fresh layer only");
+    if (b->window[layer] == 0) {
+        if (first_position != 0)
+            return b->fail(ITK_ERR_SHAPE_MISMATCH,
+                           "bulk restore first position (global layer): got " + zu(first_position) + ", expected 0");
+        if (rows > b->ring[layer])
+            return b->fail(ITK_ERR_CAPACITY, "bulk restore: " + zu(rows) + " rows exceed the context capacity of " +
+                                                 zu(b->ring[layer]));
+    } else if (rows > b->window[layer]) {
+        return b->fail(ITK_ERR_SHAPE_MISMATCH, "bulk restore rows (windowed layer): got " + zu(rows) + ", expected " +
+                                                   zu(b->window[layer]));
+    }
+    if (first_position + rows > 0xfffffff0ull) return b->fail(ITK_ERR_CAPACITY, "bulk restore: position exceeds 32 bits");
+    // Install = the append scatter at positions first_position.. (same storage-row law), without the order check.
+    for (uint64_t at = 0; at < rows; at += b->stage_rows) {
+        const uint32_t m = static_cast<uint32_t>((rows - at < b->stage_rows) ? rows - at : b->stage_rows);
+        const size_t bytes = static_cast<size_t>(m) * row * sizeof(float);
+        ITK_CUDA(b, cudaMemcpyAsync(b->d_k, keys + at * row, bytes, cudaMemcpyHostToDevice, b->stream), "k upload");
+        ITK_CUDA(b, cudaMemcpyAsync(b->d_v, values + at * row, bytes, cudaMemcpyHostToDevice, b->stream), "v upload");
+        SeqDesc d{slot, static_cast<uint32_t>(first_position + at), 0, static_cast<uint32_t>(first_position + at + m)};
+        if (int rc = run_append(b, layer, 1, &d, m, b->d_k, b->d_v)) return rc;
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "bulk restore");
+    }
+    st.appended[layer] = first_position + rows;
+    st.built = true;
+    return ITK_OK;
+}
+
+int itk_reset(itk_backend* b, uint32_t slot) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    // Ring layers read as zero-filled until written, like a fresh reference cache.
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l)
+        if (b->window[l] && b->slots[slot].appended[l] != 0) {
+            const size_t bytes = static_cast<size_t>(b->ring[l]) * b->row_len() * b->elem_bytes;
+            const size_t off = static_cast<size_t>(slot) * b->ring[l] * b->row_len() * b->elem_bytes;
+            cudaMemsetAsync(static_cast<unsigned char*>(b->layer_ptr(b->k_slab, l)) + off, 0, bytes, b->stream);
+            cudaMemsetAsync(static_cast<unsigned char*>(b->layer_ptr(b->v_slab, l)) + off, 0, bytes, b->stream);
+        }
+    drop_slot(b, slot);
+    return ITK_OK;
+}
+
+int itk_cache_checkpoint(itk_backend* b, uint32_t slot, uint64_t max_round_tokens, itk_checkpoint* out) {
+    if (!b || !out) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_slot(b, slot)) return rc;
+    SlotState& st = b->slots[slot];
+    if (!st.built)
+        return b->fail(ITK_ERR_STEP_FAILED,
+                       "cache_checkpoint: no KV state exists yet: a speculative round checkpoints after a first forward "
+                       "has built the cache (the spec's prefill), not before");
+    if (st.live)
+        return b->fail(ITK_ERR_CHECKPOINT_BUSY,
+                       "a checkpoint is already outstanding on this cache; release it before taking another");
+    if (max_round_tokens == 0) return b->fail(ITK_ERR_ZERO_DIMENSION, "max_round_tokens must be positive, got 0");
+    uint32_t smallest = 0;
+    for (uint32_t w : b->window)
+        if (w && (smallest == 0 || w < smallest)) smallest = w;
+    if (smallest && max_round_tokens > smallest)
+        return b->fail(ITK_ERR_CHECKPOINT_TOO_DEEP,
+                       "checkpoint round bound " + zu(max_round_tokens) + " exceeds the smallest sliding window " +
+                           zu(smallest) + ": a round that long would overwrite a ring slot twice and no rewind could be exact");
+    if (smallest && max_round_tokens > b->cfg.chunk_cap)
+        return b->fail(ITK_ERR_CHECKPOINT_TOO_DEEP,
+                       "checkpoint round bound " + zu(max_round_tokens) + " exceeds the ring headroom (chunk cap " +
+                           zu(b->cfg.chunk_cap) + "): discarded rows could alias rows a later query still sees");
+    st.next_serial += 1;
+    st.live = true;
+    st.live_serial = st.next_serial;
+    st.max_round = max_round_tokens;
+    st.bases = st.appended;
+    out->id = st.id;
+    out->serial = st.live_serial;
+    out->base = st.bases[0];
+    out->max_round_tokens = max_round_tokens;
+    return ITK_OK;
+}
+
+int itk_cache_rewind(itk_backend* b, uint32_t slot, const itk_checkpoint* cp, uint64_t target) {
+    if (!b || !cp) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_slot(b, slot)) return rc;
+    SlotState& st = b->slots[slot];
+    if (int rc = check_live(b, st, cp)) return rc;
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l)
+        if (target < st.bases[l] || target > st.appended[l])
+            return b->fail(ITK_ERR_REWIND_OUT_OF_RANGE, "rewind target " + zu(target) + " is outside layer " + zu(l) +
+                                                            "'s checkpoint range [" + zu(st.bases[l]) + ", " +
+                                                            zu(st.appended[l]) + "]");
+    // Rows live at position % ring and every view derives from the position, so
+    // truncation is the counter alone: rows past `target` are never read and the
+    // next append overwrites them in place.
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) st.appended[l] = target;
+    return ITK_OK;
+}
+
+int itk_cache_release(itk_backend* b, uint32_t slot, const itk_checkpoint* cp) {
+    if (!b || !cp) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_slot(b, slot)) return rc;
+    SlotState& st = b->slots[slot];
+    if (int rc = check_live(b, st, cp)) return rc;
+    st.live = false;
+    return ITK_OK;
+}
+
+int itk_snapshot_capture(itk_backend* b, uint32_t slot, itk_snapshot** out) {
+    if (!b || !out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    const SlotState& st = b->slots[slot];
+    const uint64_t tokens = st.appended[0];
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l)
+        if (st.appended[l] != tokens)
+            return b->fail(ITK_ERR_INCOHERENT_CACHE, "incoherent cache: layer 0 has appended " + zu(tokens) +
+                                                         " positions but layer " + zu(l) + " has appended " +
+                                                         zu(st.appended[l]) + "; a snapshot is one sequence");
+    itk_snapshot* s = new (std::nothrow) itk_snapshot();
+    if (!s) return b->fail(ITK_ERR_CUDA, "out of host memory");
+    s->device = b->cfg.device;
+    s->f16 = b->f16;
+    s->kv_heads = b->cfg.kv_heads;
+    s->head_dim = b->cfg.head_dim;
+    s->window = b->window;
+    s->token_count = tokens;
+    std::vector<uint32_t> layers;
+    uint64_t at = 0;
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) {
+        const uint64_t rows = b->stored(l, tokens);
+        s->first.push_back(tokens - rows);
+        s->rows.push_back(rows);
+        s->k_off.push_back(at);
+        at += rows * b->row_len();
+        s->v_off.push_back(at);
+        at += rows * b->row_len();
+        layers.push_back(l);
+    }
+    s->total_elems = at;
+    if (at) {
+        cudaError_t e = cudaMalloc(&s->data, at * b->elem_bytes);
+        if (e != cudaSuccess) {
+            delete s;
+            return b->cuda_fail(e, "snapshot allocation");
+        }
+        if (int rc = run_copy(b, slot, s->data, layers, s->first, s->rows, s->k_off, s->v_off, true)) {
+            itk_snapshot_free(s);
+            return rc;
+        }
+    }
+    b->stats.prefix_captures += 1;
+    *out = s;
+    return ITK_OK;
+}
+
+int itk_snapshot_restore(itk_backend* b, uint32_t slot, const itk_snapshot* s) {
+    if (!b || !s) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_slot(b, slot)) return rc;
+    // crates/wgpu-compute/src/session.rs:410-467: geometry, then empty, then capacity - all before any state moves.
+    if (s->window != b->window || s->kv_heads != b->cfg.kv_heads || s->head_dim != b->cfg.head_dim)
+        return b->fail(ITK_ERR_GEOMETRY_MISMATCH,
+                       "geometry mismatch: snapshot geometry (" + zu(s->window.size()) + " layers, " + zu(s->kv_heads) +
+                           " KV heads, head dim " + zu(s->head_dim) + ") differs from the session geometry (" +
+                           zu(b->window.size()) + " layers, " + zu(b->cfg.kv_heads) + " KV heads, head dim " +
+                           zu(b->cfg.head_dim) + ")");
+    if (s->f16 != b->f16 || s->device != b->cfg.device)
+        return b->fail(ITK_ERR_GEOMETRY_MISMATCH, "geometry mismatch: snapshot element type or device differs from the backend's");
+    if (s->token_count == 0)
+        return b->fail(ITK_ERR_STEP_FAILED, "prefix_install: snapshot covers zero tokens; an empty prefix installs nothing "
+                                            "and is refused rather than resetting the session to no effect");
+    if (s->token_count > b->cfg.max_context)
+        return b->fail(ITK_ERR_STEP_FAILED, "prefix_install: snapshot covers " + zu(s->token_count) +
+                                                " tokens, past the session's context capacity of " +
+                                                zu(b->cfg.max_context) + " positions");
+    if (int rc = itk_reset(b, slot)) return rc;
+    std::vector<uint32_t> layers;
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) layers.push_back(l);
+    if (int rc = run_copy(b, slot, s->data, layers, s->first, s->rows, s->k_off, s->v_off, false)) return rc;
+    SlotState& st = b->slots[slot];
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) st.appended[l] = s->token_count;
+    st.built = true;
+    b->stats.prefix_restores += 1;
+    return ITK_OK;
+}
+
+void itk_snapshot_free(itk_snapshot* s) {
+    if (!s) return;
+    if (s->data) {
+        cudaSetDevice(s->device);
+        cudaFree(s->data);
+    }
+    delete s;
+}
+
+uint64_t itk_snapshot_token_count(const itk_snapshot* s) { return s ? s->token_count : 0; }
+uint64_t itk_snapshot_payload_bytes(const itk_snapshot* s) { return s ? s->total_elems * (s->f16 ? 2 : 4) : 0; }
+
+int itk_snapshot_layer_to_host(itk_backend* b, const itk_snapshot* s, uint32_t layer, void* keys, void* values,
+                               uint64_t* first_position, uint64_t* rows) {
+    if (!b || !s) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (layer >= s->rows.size())
+        return b->fail(ITK_ERR_INVALID_LAYER, "layer " + zu(layer) + " out of range, cache has " + zu(s->rows.size()) + " layers");
+    if (first_position) *first_position = s->first[layer];
+    if (rows) *rows = s->rows[layer];
+    const size_t eb = s->f16 ? 2 : 4;
+    const size_t bytes = s->rows[layer] * s->kv_heads * s->head_dim * eb;
+    if (bytes == 0) return ITK_OK;
+    const unsigned char* base = static_cast<const unsigned char*>(s->data);
+    if (keys) ITK_CUDA(b, cudaMemcpyAsync(keys, base + s->k_off[layer] * eb, bytes, cudaMemcpyDeviceToHost, b->stream), "snapshot download");
+    if (values) ITK_CUDA(b, cudaMemcpyAsync(values, base + s->v_off[layer] * eb, bytes, cudaMemcpyDeviceToHost, b->stream), "snapshot download");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "snapshot download");
+    return ITK_OK;
+}
+
+int itk_snapshot_from_host_f32(itk_backend* b, uint64_t token_count, const uint64_t* first_position,
+                               const uint64_t* rows, const float* const* keys, const float* const* values,
+                               itk_snapshot** out) {
+    if (!b || !first_position || !rows || !keys || !values || !out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    // crates/itak-kv/src/snapshot.rs:187-236: per-layer rows and first positions follow from the token count.
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) {
+        const uint64_t want_rows = b->stored(l, token_count);
+        if (first_position[l] != token_count - want_rows)
+            return b->fail(ITK_ERR_INCONSISTENT_SNAPSHOT,
+                           "inconsistent snapshot: layer " + zu(l) + ": first stored position is " + zu(first_position[l]) +
+                               " but " + zu(token_count - want_rows) + " follows from token count " + zu(token_count));
+        if (rows[l] != want_rows)
+            return b->fail(ITK_ERR_INCONSISTENT_SNAPSHOT, "inconsistent snapshot: layer " + zu(l) + ": holds " + zu(rows[l]) +
+                                                              " rows but " + zu(want_rows) + " rows were expected");
+    }
+    itk_snapshot* s = new (std::nothrow) itk_snapshot();
+    if (!s) return b->fail(ITK_ERR_CUDA, "out of host memory");
+    s->device = b->cfg.device;
+    s->f16 = b->f16;
+    s->kv_heads = b->cfg.kv_heads;
+    s->head_dim = b->cfg.head_dim;
+    s->window = b->window;
+    s->token_count = token_count;
+    uint64_t at = 0, largest = 0;
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) {
+        const uint64_t block = rows[l] * b->row_len();
+        s->first.push_back(first_position[l]);
+        s->rows.push_back(rows[l]);
+        s->k_off.push_back(at);
+        at += block;
+        s->v_off.push_back(at);
+        at += block;
+        if (block > largest) largest = block;
+    }
+    s->total_elems = at;
+    if (at) {
+        cudaError_t e = cudaMalloc(&s->data, at * b->elem_bytes);
+        if (e != cudaSuccess) {
+            delete s;
+            return b->cuda_fail(e, "snapshot allocation");
+        }
+        float* tmp = nullptr;
+        e = cudaMalloc(&tmp, largest * sizeof(float));
+        if (e != cudaSuccess) {
+            itk_snapshot_free(s);
+            return b->cuda_fail(e, "snapshot staging allocation");
+        }
+        for (uint32_t l = 0; l < b->cfg.n_layers && e == cudaSuccess; ++l) {
+            const uint64_t block = rows[l] * b->row_len();
+            if (block == 0) continue;
+            for (int which = 0; which < 2 && e == cudaSuccess; ++which) {
+                const float* src = which ? values[l] : keys[l];
+                const uint64_t off = which ? s->v_off[l] : s->k_off[l];
+                e = cudaMemcpyAsync(tmp, src, block * sizeof(float), cudaMemcpyHostToDevice, b->stream);
+                if (e == cudaSuccess)
+                    e = itk::launch_convert(tmp, static_cast<unsigned char*>(s->data) + off * b->elem_bytes, block, b->f16,
+                                            b->stream, &b->stats.kernel_launches);
+                if (e == cudaSuccess) e = cudaStreamSynchronize(b->stream);
+            }
+        }
+        cudaFree(tmp);
+        if (e != cudaSuccess) {
+            itk_snapshot_free(s);
+            return b->cuda_fail(e, "snapshot import");
+        }
+    }
+    *out = s;
+    return ITK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,114 @@
+// Device-side contracts shared by the hot-path kernels and their launchers.
+//
+// HBM layout of the resident cache (one slab for K, one for V, per backend):
+//
+//   layer l  ->  [slot][kv_head][row][D]      row = position % ring_l
+//
+// i.e. HEAD-MAJOR inside a slot: all rows of one (slot, kv head) are one
+// contiguous stream of ring_l * D elements.  A decode CTA owns one
+// (sequence, kv head, split) and therefore streams one contiguous byte range;
+// a KV-head shard for another GPU is a contiguous slice; appends, snapshots and
+// restores are the vectorised transposes between this layout and the
+// position-major `[position][kv_head][D]` rows the callers speak.
+// ring_l is max_context on a global layer and window + chunk_cap on a sliding
+// layer: a chunk appended before its attention never evicts a row one of its
+// own queries still sees, and rows discarded by a speculative rewind never sit
+// on a row that a later query or view can reach.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace itk {
+
+constexpr int kMaxSeqsPerLaunch = 64;  // sequences described in one launch's parameters
+constexpr int kHeadsPerCta = 8;        // query heads of one GQA group handled by one CTA
+constexpr int kMaxLayersPerLaunch = 64;
+
+// One sequence of an attention / append launch.
+struct SeqDesc {
+    uint32_t slot;    // resident sequence index
+    uint32_t q_pos0;  // absolute position of the first query (and first appended) row
+    uint32_t kv_lo;   // first absolute position any row of this launch may see
+    uint32_t kv_hi;   // one past the last position (q_pos0 + rows)
+};
+
+struct LayerView {
+    const void* k;      // layer base of the K slab (element type by dtype)
+    const void* v;      // layer base of the V slab
+    uint32_t ring;      // rows per (slot, head) stream
+    uint32_t window;    // 0 = global layer, else the attention window
+    uint32_t kv_heads;  // heads resident in this backend
+    uint32_t head_dim;
+};
+
+struct AttnLaunch {
+    LayerView layer;
+    const float* q;          // [n_seqs][rows][q_heads][D]
+    float* out;              // [n_seqs][rows][q_heads][D]
+    float* part_o;           // [unit][hy][split][8][D] unnormalised partial outputs
+    float* part_ml;          // [unit][hy][split][8][2] running max (log2 domain) and sum
+    unsigned int* tickets;   // [unit][hy] arrival counters, zero between launches
+    uint32_t q_heads;
+    uint32_t group;          // q_heads / kv_heads
+    uint32_t gchunks;        // ceil(group / 8): head chunks per kv head
+    uint32_t rows;           // query rows per sequence
+    uint32_t n_seqs;
+    uint32_t splits;         // CTAs along the key range
+    float scale;             // score scale, 1/sqrt(D) by default
+    SeqDesc seq[kMaxSeqsPerLaunch];
+};
+
+struct AppendLaunch {
+    void* k;  // layer base of the K slab
+    void* v;
+    const float* k_src;  // [n_seqs][rows][kv_heads][D]
+    const float* v_src;
+    uint32_t ring, kv_heads, head_dim, rows, n_seqs;
+    SeqDesc seq[kMaxSeqsPerLaunch];
+};
+
+// One layer of a snapshot gather / restore scatter.
+struct CopyLayer {
+    unsigned long long slab_off;  // element offset of this layer inside the K (= V) slab
+    unsigned long long snap_k;    // element offset of the layer's K block inside the snapshot buffer
+    unsigned long long snap_v;    // ... and of its V block
+    uint32_t ring;
+    uint32_t first_pos;  // absolute position of the block's first row
+    uint32_t rows;
+    uint32_t _pad;
+};
+
+struct CopyLaunch {
+    void* k_slab;
+    void* v_slab;
+    void* snap;          // snapshot buffer (element type = cache element type)
+    uint32_t slot, kv_heads, head_dim, n_layers;
+    uint32_t elem_bytes;
+    uint32_t to_snapshot;  // 1 = gather slab -> snapshot, 0 = scatter snapshot -> slab
+    unsigned long long total_vec;  // 16-byte vectors over all layers (K and V)
+    unsigned long long vec_prefix[kMaxLayersPerLaunch + 1];  // running K-vector counts per layer
+    CopyLayer layer[kMaxLayersPerLaunch];
+};
+
+// ---- launchers (defined next to their kernels) -------------------------------
+// Every launcher returns the CUDA error of the launch and adds the number of
+// kernels it launched to *launches.
+
+cudaError_t launch_append(const AppendLaunch& p, bool f16, cudaStream_t s, uint64_t* launches);
+// f32 -> cache element type, flat (used to import f32 snapshot rows).
+cudaError_t launch_convert(const float* src, void* dst, size_t n, bool f16, cudaStream_t s, uint64_t* launches);
+// Flash-decode over an f16 cache, rows == 1, head_dim 64 or 128 (tensor-core path).
+cudaError_t launch_decode_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);
+bool decode_f16_supported(uint32_t head_dim, uint32_t rows);
+// Multi-row causal attention over an f16 cache (chunked prefill / speculative verify).
+cudaError_t launch_verify_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);
+bool verify_f16_supported(uint32_t head_dim, uint32_t rows, uint32_t group);
+// General kernel: any head_dim <= 256, any rows, f32 or f16 cache (CUDA cores, f32 math).
+cudaError_t launch_attn_general(const AttnLaunch& p, bool f16, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_snapshot_copy(const CopyLaunch& p, cudaStream_t s, uint64_t* launches);
+// One-time per-device kernel attribute setup (dynamic shared memory opt-in).
+cudaError_t configure_kernels();
+
+}  // namespace itk

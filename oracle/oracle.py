@@ -639,18 +639,12 @@ class CpuCompute:
 
 
 # --- deterministic generators used by the reference's fixtures ---------------------------
-_M64 = (1 << 64) - 1
-
-
 def lcg(seed: int, count: int) -> np.ndarray:
     """f32 in [-0.5, 0.5): state = max(seed, 1); state = state*A + C; (state >> 40) / 2^24 - 0.5.
 
     The generator of crates/wgpu-compute/tests/fused_kernels.rs:45-55 and
     crates/itak-kv/tests/restore_fixture.rs:22-30.
     """
-    state = max(seed, 1) & _M64
     out = np.empty(count, dtype=np.float32)
-    for i in range(count):
-        state = (state * 6364136223846793005 + 1442695040888963407) & _M64
-        out[i] = np.float32(np.float32(state >> 40) / np.float32(1 << 24)) - np.float32(0.5)
+    lib().orc_lcg(C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _sz(count), _fp(out))
     return out

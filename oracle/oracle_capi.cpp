@@ -249,6 +249,19 @@ int orc_attention_units(size_t n_units, void* const* caches, const uint64_t* lay
     return done({});
 }
 
+// ---- the reference fixtures' generator ----------------------------------------
+// f32 in [-0.5, 0.5): state = max(seed, 1); per value state = state * A + C
+// (wrapping u64), value = ((state >> 40) as f32) / 2^24 - 0.5
+// (crates/wgpu-compute/tests/fused_kernels.rs:45-55,
+//  crates/itak-kv/tests/restore_fixture.rs:22-30).
+void orc_lcg(uint64_t seed, size_t count, float* out) {
+    uint64_t state = seed < 1 ? 1 : seed;
+    for (size_t i = 0; i < count; ++i) {
+        state = state * 6364136223846793005ull + 1442695040888963407ull;
+        out[i] = static_cast<float>(static_cast<uint32_t>(state >> 40)) / static_cast<float>(1u << 24) - 0.5f;
+    }
+}
+
 // ---- hashes ----------------------------------------------------------------
 uint64_t orc_checksum(const uint8_t* bytes, size_t n) { return checksum(bytes, n); }
 uint64_t orc_prefix_hash(const uint32_t* tokens, size_t n) { return prefix_hash(tokens, n); }
