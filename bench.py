@@ -145,48 +145,62 @@ def run_reference(args):
 # clocks
 # ---------------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons through NVML (read-only) every ~20 ms."""
+
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+               "hw_power_brake_slowdown": 0x80}
 
     def __init__(self, index: int):
         self.index = index
-        self.samples = []
+        self.sm, self.reason_bits, self.power = [], 0, []
+        self.max_sm = None
         self._stop = threading.Event()
         self._thread = None
+        self._h = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._h = None
+
+    @staticmethod
+    def _physical_index(index: int) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            parts = [p for p in vis.split(",") if p.strip()]
+            if index < len(parts) and parts[index].strip().isdigit():
+                return int(parts[index])
+        return index
 
     def _loop(self):
+        nv = self._nv
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                if out.returncode == 0 and out.stdout.strip():
-                    self.samples.append([p.strip() for p in out.stdout.strip().splitlines()[0].split(",")])
+                self.sm.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.02)
 
     def start(self):
+        if self._h is None:
+            return
         self._thread = threading.Thread(target=self._loop, daemon=True)
         self._thread.start()
 
     def stop(self) -> dict:
         self._stop.set()
         if self._thread:
-            self._thread.join(timeout=6)
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            try:
-                sm.append(float(s[0]))
-                mx.append(float(s[1]))
-                for name, v in zip(names, s[3:7]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
-            except Exception:
-                continue
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+            self._thread.join(timeout=2)
+        reasons = sorted(name for name, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.max_sm,
+                "reasons": reasons, "samples": len(self.sm),
+                "power_w_max": max(self.power) if self.power else None}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -220,7 +234,9 @@ def run_ours(args):
 
     be = CudaCompute(layers, hq_l, hkv_l, d, n_slots=seqs, max_context=ctx + headroom, chunk_cap=1,
                      kv_dtype=KvDtype.F16, device=local_rank)
-    stream = torch.cuda.current_stream()
+    # One non-default stream carries the kernels, the NCCL collectives and the timing events.
+    stream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
 
     # ---- prefill the resident cache with seeded N(0,1) rows, generated on the device -----------------

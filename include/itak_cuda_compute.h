@@ -119,8 +119,9 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out);
 void itk_backend_destroy(itk_backend* b);
 /* Text of the last refusal on `b`; with b == NULL, of the last failed create. */
 const char* itk_last_error(const itk_backend* b);
-/* Work is issued on `cuda_stream` (a cudaStream_t) from now on; NULL = the
- * backend's own stream.  The caller orders its own work against it. */
+/* Work is issued on `cuda_stream` (a cudaStream_t) from now on; NULL selects
+ * the backend's own non-blocking stream again (pass cudaStreamLegacy for
+ * CUDA's default stream).  The caller orders its own work against it. */
 int itk_set_stream(itk_backend* b, void* cuda_stream);
 int itk_synchronize(itk_backend* b);
 int itk_get_stats(const itk_backend* b, itk_stats* out);

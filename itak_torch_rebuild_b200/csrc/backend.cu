@@ -22,6 +22,8 @@
 
 namespace itk {
 cudaError_t configure_decode_f16();
+cudaError_t configure_verify_f16();
+uint32_t verify_pair_chunks(uint32_t rows, uint32_t group);
 }
 
 namespace {
@@ -87,6 +89,7 @@ struct itk_backend {
     itk_stats stats{};
     int sm_count = 148;
     int forced_splits = 0;
+    bool force_general = false;  // ITK_FORCE_GENERAL=1: multi-row launches take the CUDA-core kernel (A/B checks)
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
@@ -131,12 +134,12 @@ int check_layer(const itk_backend* b, uint32_t layer) {
 
 // KV splits for a decode launch: minimise waves x (tiles per CTA + fixed cost)
 // over the CTA slots the device offers (2 resident CTAs per SM).
-uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uint32_t tile) {
+uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uint32_t tile, uint64_t scratch_mult = 1) {
     if (b->forced_splits > 0) {
         uint64_t s = static_cast<uint64_t>(b->forced_splits);
         const uint64_t by_len = (n_max + tile - 1) / tile;
         if (s > by_len) s = by_len;
-        if (s * cells > kPartCellSplits) s = kPartCellSplits / cells;
+        if (s * cells * scratch_mult > kPartCellSplits) s = kPartCellSplits / (cells * scratch_mult);
         return static_cast<uint32_t>(s < 1 ? 1 : s);
     }
     const uint64_t slots = static_cast<uint64_t>(b->sm_count) * 2;
@@ -144,7 +147,7 @@ uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uin
     if (max_s < 1) max_s = 1;
     if (max_s > 256) max_s = 256;
     if (cells == 0) return 1;
-    if (max_s * cells > kPartCellSplits) max_s = kPartCellSplits / cells;
+    if (max_s * cells * scratch_mult > kPartCellSplits) max_s = kPartCellSplits / (cells * scratch_mult);
     if (max_s < 1) max_s = 1;
     uint64_t best = 1;
     double best_cost = 1e300;
@@ -213,7 +216,8 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
     const uint32_t D = b->cfg.head_dim;
     const uint32_t HY = b->cfg.kv_heads * b->gchunks;
     const bool decode = b->f16 && itk::decode_f16_supported(D, rows);
-    // grid.z carries n_seqs * rows and is limited to 65535
+    const bool verify = b->f16 && !decode && !b->force_general && itk::verify_f16_supported(D, rows, b->group);
+    // grid.z carries n_seqs * rows (general kernel) and is limited to 65535
     uint32_t per_launch = itk::kMaxSeqsPerLaunch;
     while (per_launch > 1 && static_cast<uint64_t>(per_launch) * rows > 65535) per_launch >>= 1;
     if (static_cast<uint64_t>(rows) > 65535)
@@ -238,18 +242,24 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
             p.seq[i] = seqs[at + i];
             const uint64_t span = p.seq[i].kv_hi - p.seq[i].kv_lo;
             if (span > n_max) n_max = span;
-            keys += span;  // upper bound for multi-row launches; exact for decode
+            keys += span;  // every stored row the launch can see is streamed once per KV head
         }
-        const uint64_t cells = static_cast<uint64_t>(m) * rows * HY;
+        // A "cell" is one (unit, head chunk) whose splits are merged: a (sequence, row) for the decode and
+        // general kernels, a (sequence, block of 32 row-head pairs) for the verify kernel, which needs four
+        // times the scratch per (cell, split).
+        const uint64_t cells = verify ? static_cast<uint64_t>(m) * HY * itk::verify_pair_chunks(rows, b->group)
+                                      : static_cast<uint64_t>(m) * rows * HY;
         if (cells > b->ticket_cells)
             return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(cells) + " (row, head) cells exceed the scratch of " +
                                                  zu(b->ticket_cells));
-        p.splits = choose_splits(b, cells, n_max, decode ? 64 : 128);
+        p.splits = choose_splits(b, cells, n_max, (decode || verify) ? 64 : 128, verify ? 4 : 1);
         b->stats.last_splits = p.splits;
         b->stats.kv_bytes_read += keys * b->cfg.kv_heads * D * 2ull * b->elem_bytes;
         const long ev = prof_begin(b, 0);
         if (decode)
             ITK_CUDA(b, itk::launch_decode_f16(p, b->stream, &b->stats.kernel_launches), "decode attention launch");
+        else if (verify)
+            ITK_CUDA(b, itk::launch_verify_f16(p, b->stream, &b->stats.kernel_launches), "verify attention launch");
         else
             ITK_CUDA(b, itk::launch_attn_general(p, b->f16, b->stream, &b->stats.kernel_launches),
                      "attention launch");
@@ -456,6 +466,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
         return cuda_refuse(cudaErrorNoKernelImageForDevice, "this library carries sm_100a kernels only");
     b->sm_count = prop.multiProcessorCount;
     e = itk::configure_decode_f16();
+    if (e == cudaSuccess) e = itk::configure_verify_f16();
     if (e != cudaSuccess) return cuda_refuse(e, "kernel attribute setup");
     e = cudaStreamCreateWithFlags(&b->own_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) return cuda_refuse(e, "cudaStreamCreate");
@@ -493,6 +504,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     b->slots.resize(cfg->n_slots);
     for (uint32_t s = 0; s < cfg->n_slots; ++s) drop_slot(b, s);
     if (const char* env = std::getenv("ITK_DECODE_SPLITS")) b->forced_splits = std::atoi(env);
+    if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     *out = b;
     return ITK_OK;
 }
@@ -685,9 +697,11 @@ int itk_append_rows(itk_backend* b, uint32_t slot, uint32_t layer, const float* 
     if (b->window[layer] == 0 && start + rows > b->ring[layer])
         return b->fail(ITK_ERR_CAPACITY, "append: position " + zu(start + rows) + " is past the slot's context capacity of " +
                                              zu(b->ring[layer]) + " positions");
-    if (b->window[layer] != 0 && rows > b->ring[layer])
-        return b->fail(ITK_ERR_CAPACITY, "append: " + zu(rows) + " rows exceed the ring of " + zu(b->ring[layer]));
-    for (uint32_t at = 0; at < rows; at += static_cast<uint32_t>(b->stage_rows)) {
+    // On a ring layer only the newest `ring` rows of a long append can survive; the older ones would be
+    // overwritten inside the same call, so they are skipped (the reference evicts them just the same).
+    uint32_t first_row = 0;
+    if (b->window[layer] != 0 && rows > b->ring[layer]) first_row = rows - b->ring[layer];
+    for (uint32_t at = first_row; at < rows; at += static_cast<uint32_t>(b->stage_rows)) {
         const uint32_t m = (rows - at < b->stage_rows) ? rows - at : static_cast<uint32_t>(b->stage_rows);
         const size_t bytes = static_cast<size_t>(m) * b->row_len() * sizeof(float);
         ITK_CUDA(b, cudaMemcpyAsync(b->d_k, k + static_cast<size_t>(at) * b->row_len(), bytes, cudaMemcpyHostToDevice,
