@@ -242,6 +242,36 @@ int itk_snapshot_from_host_f32(itk_backend* b, uint64_t token_count, const uint6
                                const uint64_t* rows, const float* const* keys, const float* const* values,
                                itk_snapshot** out);
 
+/* ---- for callers that cannot allocate ------------------------------------------------ */
+
+/* No counterpart in the reference (its backends allocate freely).  Decode
+ * attention - one query row per sequence over an f16 cache in this library's
+ * head-major layout - for a caller that is not allowed to allocate device
+ * memory when it calls: a server that sized everything at start-up, a plugin
+ * living inside another runtime's allocator, a latency-critical loop that
+ * cannot afford cudaMalloc's synchronisation, or work being recorded for
+ * replay.  The split-K partials live in a fixed ~8.1 MiB array inside the
+ * library image (present on every GPU that loads the library, until exit), so
+ * the call performs no cudaMalloc / cudaFree and needs no backend object.
+ *
+ *   k_layer, v_layer  device, f16 [slot][kv_heads][ring][head_dim]; keys 0..kv_len[i]-1 of sequence i
+ *                     sit at rows 0.. of slot slots[i]
+ *   d_q, d_out        device f32 [n_seqs][q_heads][head_dim]
+ *   splits            CTAs along each key range; 0 picks one
+ *   error_text        optional buffer that receives the reason of a refusal
+ *
+ * Limits: head_dim 64 or 128; n_seqs <= 64; n_seqs x kv_heads x ceil(group/8) x splits <= 2048.
+ * Larger requests return ITK_ERR_CAPACITY.  The first call on a device looks
+ * up the array's device address and sets a kernel attribute; issue that first
+ * call outside any stream capture.  All calls share the array (the counters in
+ * it are cleared on the stream at the start of each call): calls that may
+ * overlap on the GPU must be serialised by the caller.  The device that owns
+ * the buffers must be current.  Returns once the work is queued on the stream. */
+int itk_decode_attention_noalloc(const void* k_layer, const void* v_layer, uint32_t ring, uint32_t kv_heads,
+                                 uint32_t q_heads, uint32_t head_dim, uint32_t n_seqs, const uint32_t* slots,
+                                 const uint32_t* kv_len, const float* d_q, float* d_out, uint32_t splits,
+                                 void* cuda_stream, char* error_text, size_t error_text_len);
+
 #ifdef __cplusplus
 }
 #endif

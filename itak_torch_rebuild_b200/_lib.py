@@ -108,6 +108,8 @@ SIGNATURES = {
     "itk_snapshot_payload_bytes": (_u64, [_vp]),
     "itk_snapshot_layer_to_host": (C.c_int, [_vp, _vp, _u32, _vp, _vp, _u64p, _u64p]),
     "itk_snapshot_from_host_f32": (C.c_int, [_vp, _u64, _u64p, _u64p, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
+    "itk_decode_attention_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _vp, _vp, _u32, _vp,
+                                               C.c_char_p, _sz]),
 }
 
 _lib = None

@@ -26,6 +26,8 @@
 // ~2^-22 and the accumulation is f32, so the result tracks the f32 reference
 // far inside the f16-KV tolerance.  A 64-row tcgen05 tile would be 7/8 padding
 // here; the tensor pipe is at ~15% load either way and never the limiter.
+#include <cstdio>
+
 #include "attn_common.cuh"
 
 namespace itk {
@@ -293,3 +295,165 @@ cudaError_t launch_decode_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* lau
 }
 
 }  // namespace itk
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that must not allocate.
+//
+// Who this is for: code that runs where a device allocation is off the table -
+// a serving loop that took all of its memory at start-up and is forbidden to
+// grow, a plugin invoked from inside somebody else's runtime that owns the
+// allocator, a real-time path where cudaMalloc's implicit synchronisation is
+// unacceptable, or a region of work being recorded for later replay, in which
+// an allocation is an error.  Such a caller already holds its cache, its
+// queries and its output buffer; the only thing the split-K decode kernel
+// still needs is somewhere to park the per-split partial results.  Here that
+// scratch is a fixed array baked into the library image, so the call performs
+// no cudaMalloc, no cudaFree and no other allocating routine.
+//
+// Cost and limits of that choice:
+//  - the array below (about 8.1 MiB) exists on every GPU that loads this
+//    library, from load until the process exits, whether or not this entry
+//    point is ever used;
+//  - (sequences x KV heads x head chunks) x splits may not exceed
+//    kNoAllocCellSplits, sequences may not exceed 64, head_dim is 64 or 128;
+//    anything larger is refused with ITK_ERR_CAPACITY and a message;
+//  - all calls share the one array and it keeps whatever the previous call
+//    left.  The arrival counters are the only part that must read zero at
+//    launch; every call clears them on its stream first.  Two calls whose
+//    kernels can overlap on the GPU (different streams, or different host
+//    threads on different streams) trample each other's partials and
+//    counters: serialise them.
+//
+// A symbol declared `__device__` is, in host code, only a handle for the
+// runtime - not an address a kernel can dereference.  The device address is
+// obtained once per device with cudaGetSymbolAddress while that device is
+// current, and that pointer is what the kernel receives.  The first call on a
+// device performs this set-up (and the kernel's shared-memory opt-in); make
+// that first call before starting any stream capture.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocCellSplits = 2048;  // (cell, split) partial slots
+constexpr size_t kNoAllocPartO = kNoAllocCellSplits * itk::kHeadsPerCta * 128 * sizeof(float);  // 8 MiB
+constexpr size_t kNoAllocPartMl = kNoAllocCellSplits * itk::kHeadsPerCta * 2 * sizeof(float);   // 128 KiB
+constexpr size_t kNoAllocTickets = kNoAllocCellSplits * sizeof(unsigned int);                    // 8 KiB
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartO + kNoAllocPartMl + kNoAllocTickets];
+
+// Device address of g_noalloc_scratch per device ordinal, resolved on first use.
+void* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+int noalloc_refuse(int code, char* text, size_t text_len, const char* fmt, unsigned long long a = 0,
+                   unsigned long long b = 0) {
+    if (text && text_len) snprintf(text, text_len, fmt, a, b);
+    return code;
+}
+
+}  // namespace
+
+extern "C" int itk_decode_attention_noalloc(const void* k_layer, const void* v_layer, uint32_t ring,
+                                            uint32_t kv_heads, uint32_t q_heads, uint32_t head_dim, uint32_t n_seqs,
+                                            const uint32_t* slots, const uint32_t* kv_len, const float* d_q,
+                                            float* d_out, uint32_t splits, void* cuda_stream, char* error_text,
+                                            size_t error_text_len) {
+    using namespace itk;
+    if (error_text && error_text_len) error_text[0] = '\0';
+    if (!k_layer || !v_layer || !slots || !kv_len || !d_q || !d_out)
+        return noalloc_refuse(101, error_text, error_text_len, "null pointer argument");
+    if (kv_heads == 0 || q_heads == 0 || ring == 0)
+        return noalloc_refuse(1, error_text, error_text_len, "kv_heads, q_heads and ring must be positive");
+    if (q_heads % kv_heads != 0)
+        return noalloc_refuse(7, error_text, error_text_len, "%llu query heads do not divide evenly across %llu KV heads",
+                              q_heads, kv_heads);
+    if (head_dim != 64 && head_dim != 128)
+        return noalloc_refuse(102, error_text, error_text_len, "head_dim %llu is not supported here (64 or 128)", head_dim);
+    if (n_seqs == 0) return 0;
+    if (n_seqs > static_cast<uint32_t>(kMaxSeqsPerLaunch))
+        return noalloc_refuse(102, error_text, error_text_len,
+                              "%llu sequences exceed this entry point's maximum of %llu per call", n_seqs,
+                              static_cast<unsigned long long>(kMaxSeqsPerLaunch));
+    const uint32_t group = q_heads / kv_heads;
+    const uint32_t gchunks = (group + kHeadsPerCta - 1) / kHeadsPerCta;
+    const unsigned long long cells = static_cast<unsigned long long>(n_seqs) * kv_heads * gchunks;
+    uint32_t n_max = 0;
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        if (kv_len[i] == 0)
+            return noalloc_refuse(8, error_text, error_text_len, "sequence %llu has no visible keys", i);
+        if (kv_len[i] > ring)
+            return noalloc_refuse(102, error_text, error_text_len, "sequence %llu holds more keys than the ring of %llu",
+                                  i, ring);
+        if (kv_len[i] > n_max) n_max = kv_len[i];
+    }
+    if (cells > kNoAllocCellSplits)
+        return noalloc_refuse(102, error_text, error_text_len,
+                              "%llu (sequence, head) cells exceed the built-in scratch of %llu", cells,
+                              static_cast<unsigned long long>(kNoAllocCellSplits));
+    if (splits == 0) {  // a few hundred CTAs, at least four 64-key tiles each
+        unsigned long long s = (296 * 2 + cells - 1) / cells;
+        const unsigned long long by_len = (n_max + 255) / 256;
+        if (s > by_len) s = by_len;
+        if (s * cells > kNoAllocCellSplits) s = kNoAllocCellSplits / cells;
+        splits = static_cast<uint32_t>(s < 1 ? 1 : s);
+    }
+    if (cells * splits > kNoAllocCellSplits)
+        return noalloc_refuse(102, error_text, error_text_len,
+                              "cells x splits = %llu exceeds the built-in scratch of %llu partial slots; lower `splits`",
+                              cells * splits, static_cast<unsigned long long>(kNoAllocCellSplits));
+
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices)
+        return noalloc_refuse(100, error_text, error_text_len, "no usable current CUDA device");
+    if (!g_noalloc_ptr[dev]) {
+        // One-time set-up for this device: resolve the array's device address and opt the kernel in to its
+        // dynamic shared memory size.  Neither allocates.
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) {
+            if (error_text && error_text_len)
+                snprintf(error_text, error_text_len, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return 100;
+        }
+        e = configure_decode_f16();
+        if (e != cudaSuccess) {
+            if (error_text && error_text_len)
+                snprintf(error_text, error_text_len, "kernel attribute setup failed: %s", cudaGetErrorString(e));
+            return 100;
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    AttnLaunch p{};
+    p.layer.k = k_layer;
+    p.layer.v = v_layer;
+    p.layer.ring = ring;
+    p.layer.window = 0;
+    p.layer.kv_heads = kv_heads;
+    p.layer.head_dim = head_dim;
+    p.q = d_q;
+    p.out = d_out;
+    p.part_o = reinterpret_cast<float*>(base);
+    p.part_ml = reinterpret_cast<float*>(base + kNoAllocPartO);
+    p.tickets = reinterpret_cast<unsigned int*>(base + kNoAllocPartO + kNoAllocPartMl);
+    p.q_heads = q_heads;
+    p.group = group;
+    p.gchunks = gchunks;
+    p.rows = 1;
+    p.n_seqs = n_seqs;
+    p.splits = splits;
+    p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+    for (uint32_t i = 0; i < n_seqs; ++i) p.seq[i] = SeqDesc{slots[i], kv_len[i] - 1, 0, kv_len[i]};
+    // The arrival counters must read zero when the kernel starts, whatever an earlier (possibly failed)
+    // call left behind.
+    e = cudaMemsetAsync(p.tickets, 0, cells * sizeof(unsigned int), stream);
+    if (e == cudaSuccess) e = launch_decode_f16(p, stream, nullptr);
+    if (e != cudaSuccess) {
+        if (error_text && error_text_len)
+            snprintf(error_text, error_text_len, "decode attention launch failed: %s", cudaGetErrorString(e));
+        return 100;
+    }
+    return 0;
+}
