@@ -67,21 +67,29 @@ __device__ __forceinline__ void split_half(float x, __half& hi, __half& lo) {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-// CTA epilogue.  On entry the CTA's own result for its key range sits in shared
-// memory: fo[8][D] (unnormalised sum of p * v), fm[8] (running max, log2
-// domain, -inf when the range was empty) and fl[8] (sum of p).  With one split
-// the output is written directly.  Otherwise the partial goes to global
-// scratch, the CTA takes a ticket, and the CTA that draws the last ticket
-// merges every split (log-sum-exp) and writes the output; nobody waits.
+constexpr int kMaxSplits = 256;  // upper bound on the partials merged for one cell (sizes the merge scratch)
+
+// CTA epilogue for one cell = (unit, head chunk).  On entry the CTA's own result
+// for its part of the cell's key range sits in shared memory: fo[8][D]
+// (unnormalised sum of p * v), fm[8] (running max, log2 domain, -inf when the
+// part was empty) and fl[8] (sum of p).  `n_parts` CTAs share the cell and this
+// one is number `part`.  With one part the output is written directly.
+// Otherwise the partial goes to global scratch (p.splits slots per cell), the
+// CTA takes a ticket, and the CTA that draws the last ticket merges every part
+// (log-sum-exp) and writes the output; nobody waits.
+// The merge is two passes so that its global loads are independent of each
+// other: first the (max, sum) pairs of every split become per-split weights in
+// `wscratch` (shared memory, 2 * MAXP * 8 + 8 floats), then every output channel
+// is a weighted sum over splits with several loads in flight.
 // The ticket counter is left at zero for the next launch.
-template <int THREADS>
-__device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t split,
-                                            uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
-                                            const float* fm, const float* fl, int* s_flag) {
+template <int THREADS, int MAXP>
+__device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t n_parts,
+                                            uint32_t part, uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
+                                            const float* fm, const float* fl, int* s_flag, float* wscratch) {
     const uint32_t tid = threadIdx.x;
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
     float* out = p.out + (static_cast<size_t>(unit) * p.q_heads + head0) * D;
-    if (p.splits == 1) {
+    if (n_parts == 1) {
         for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
             const uint32_t h = idx / D;
             out[idx] = fo[idx] / fl[h];
@@ -89,8 +97,8 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
         return;
     }
     const size_t cell = static_cast<size_t>(unit) * HY + hy;
-    float* po = p.part_o + (cell * p.splits + split) * (kHeadsPerCta * D);
-    float* pml = p.part_ml + (cell * p.splits + split) * (kHeadsPerCta * 2);
+    float* po = p.part_o + (cell * p.splits + part) * (kHeadsPerCta * D);
+    float* pml = p.part_ml + (cell * p.splits + part) * (kHeadsPerCta * 2);
     for (uint32_t idx = tid; idx < nh * D; idx += THREADS) po[idx] = fo[idx];
     if (tid < nh) {
         pml[2 * tid] = fm[tid];
@@ -100,29 +108,58 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
     __syncthreads();
     if (tid == 0) {
         const unsigned int ticket = atomicAdd(p.tickets + cell, 1u);
-        *s_flag = (ticket == p.splits - 1) ? 1 : 0;
+        *s_flag = (ticket == n_parts - 1) ? 1 : 0;
     }
     __syncthreads();
     if (*s_flag == 0) return;
     __threadfence();
     const float* all_o = p.part_o + cell * p.splits * (kHeadsPerCta * D);
     const float* all_ml = p.part_ml + cell * p.splits * (kHeadsPerCta * 2);
+    float* w_m = wscratch;                        // [splits][8] maxima, then weights
+    float* w_l = wscratch + MAXP * kHeadsPerCta;  // [parts][8] sums
+    float* inv_l = w_l + MAXP * kHeadsPerCta;     // [8]
+    for (uint32_t i = tid; i < n_parts * kHeadsPerCta; i += THREADS) {
+        const uint32_t h = i % kHeadsPerCta;
+        float ms = -INFINITY, ls = 0.f;
+        if (h < nh) {
+            ms = __ldcg(all_ml + 2 * i);
+            ls = __ldcg(all_ml + 2 * i + 1);
+        }
+        w_m[i] = ms;
+        w_l[i] = ls;
+    }
+    __syncthreads();
+    if (tid < nh) {
+        float M = -INFINITY;
+        for (uint32_t s = 0; s < n_parts; ++s) M = fmaxf(M, w_m[s * kHeadsPerCta + tid]);
+        float L = 0.f;
+        for (uint32_t s = 0; s < n_parts; ++s) {
+            const float ms = w_m[s * kHeadsPerCta + tid];
+            const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+            w_m[s * kHeadsPerCta + tid] = w;
+            L += w * w_l[s * kHeadsPerCta + tid];
+        }
+        inv_l[tid] = 1.f / L;
+    }
+    __syncthreads();
     for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
         const uint32_t h = idx / D;
-        float M = -INFINITY, L = 0.f, O = 0.f;
-        for (uint32_t s = 0; s < p.splits; ++s) {
-            const float ms = __ldcg(all_ml + s * (kHeadsPerCta * 2) + 2 * h);
-            if (ms == -INFINITY) continue;
-            const float ls = __ldcg(all_ml + s * (kHeadsPerCta * 2) + 2 * h + 1);
-            const float os = __ldcg(all_o + static_cast<size_t>(s) * (kHeadsPerCta * D) + idx);
-            const float Mn = fmaxf(M, ms);
-            const float a = fast_exp2(M - Mn);  // exp2(-inf) = 0 on the first live split
-            const float b = fast_exp2(ms - Mn);
-            O = O * a + os * b;
-            L = L * a + ls * b;
-            M = Mn;
+        const float* src = all_o + idx;
+        float acc = 0.f;
+        uint32_t s = 0;
+        for (; s + 4 <= n_parts; s += 4) {
+            const float o0 = __ldcg(src + static_cast<size_t>(s) * (kHeadsPerCta * D));
+            const float o1 = __ldcg(src + static_cast<size_t>(s + 1) * (kHeadsPerCta * D));
+            const float o2 = __ldcg(src + static_cast<size_t>(s + 2) * (kHeadsPerCta * D));
+            const float o3 = __ldcg(src + static_cast<size_t>(s + 3) * (kHeadsPerCta * D));
+            acc += w_m[s * kHeadsPerCta + h] * o0;
+            acc += w_m[(s + 1) * kHeadsPerCta + h] * o1;
+            acc += w_m[(s + 2) * kHeadsPerCta + h] * o2;
+            acc += w_m[(s + 3) * kHeadsPerCta + h] * o3;
         }
-        out[idx] = O / L;
+        for (; s < n_parts; ++s)
+            acc += w_m[s * kHeadsPerCta + h] * __ldcg(src + static_cast<size_t>(s) * (kHeadsPerCta * D));
+        out[idx] = acc * inv_l[h];
     }
     if (tid == 0) p.tickets[cell] = 0u;
 }

@@ -5,17 +5,25 @@
 // way the K6 flash f16 shader does (crates/wgpu-compute/src/kernels/k6_attention.rs:642-914):
 // keys and values are upconverted exactly, all arithmetic accumulates in f32.
 //
-// Work split (what the reference kernels lack): one CTA per
-// (sequence, KV head, split of the key range).  All query heads of the GQA
-// group share every K/V tile, so each cache byte crosses HBM once per step.
-// The key range is cut into `splits` CTAs; each writes an (m, l, o) partial
-// and the last CTA to arrive merges them (see finish_unit).
+// Work split (what the reference kernels lack).  A "cell" is one
+// (sequence, KV head chunk): all query heads of the GQA group share every K/V
+// tile, so each cache byte crosses HBM once per step.  The launch's tiles
+// (64 keys each), laid end to end over all cells, are cut into equal
+// contiguous runs, one per persistent CTA - two CTAs per SM, every SM busy
+// until the last tile whatever the batch's context lengths are.  A CTA whose
+// run crosses a cell boundary finishes its part of the first cell and moves
+// on; each part writes an (m, l, o) partial and the last CTA to arrive at a
+// cell merges them (finish_unit).  Nobody waits for anybody.
 //
 // Inside a CTA each of the 4 warps owns a private cp.async pipeline over its
-// own 16-key slice of every 64-key tile: 16-byte coalesced loads into
-// XOR-swizzled shared memory, STAGES tiles in flight, no CTA-wide barrier in
-// the main loop.  The cache is head-major, so a CTA's loads walk one contiguous
-// stream.
+// own 16-key slice of every tile: 16-byte coalesced loads into XOR-swizzled
+// shared memory, STAGES tiles in flight, no CTA-wide barrier except where a
+// cell ends.  The cache is head-major, so a CTA's loads walk contiguous streams.
+//
+// The step's new K/V row can ride along (AttnLaunch::k_new): the one warp whose
+// slice holds position kv_hi - 1 converts the f32 row (round-to-nearest-even,
+// the append kernel's function), stores it to the cache and drops it into its
+// own staged tile, which saves the separate append launch of a decode step.
 //
 // Bound: HBM.  A cache element (2 B) feeds 2 * group MACs, 4 FMA/B at group 8;
 // at 6.5 TB/s that is ~70% of the SM's fp32 FMA rate before counting the
@@ -25,10 +33,11 @@
 // group of 8 would otherwise leave as padding.  The products are then exact to
 // ~2^-22 and the accumulation is f32, so the result tracks the f32 reference
 // far inside the f16-KV tolerance.  A 64-row tcgen05 tile would be 7/8 padding
-// here; the tensor pipe is at ~15% load either way and never the limiter.
+// here; the tensor pipe is at ~18% load either way and never the limiter.
 #include <cstdio>
 
 #include "attn_common.cuh"
+#include "kv_convert.cuh"
 
 namespace itk {
 
@@ -37,6 +46,28 @@ namespace {
 constexpr int kDecodeThreads = 128;
 constexpr int kDecodeWarps = 4;
 constexpr int kTileKeys = 64;  // keys per CTA tile = 16 per warp
+
+// A walker's place in the launch's tile sequence (warp-uniform).
+struct TileCursor {
+    uint32_t seq, hy, tile;  // current cell (sequence, head chunk) and tile inside it
+    uint32_t T;              // tiles of the current sequence
+    uint32_t n;              // visible keys of the current sequence
+    uint32_t s0;             // storage row of its first visible key
+    uint32_t slot;
+};
+
+template <int D, int STAGES>
+__host__ __device__ constexpr size_t decode_pipe_bytes() {
+    return static_cast<size_t>(STAGES) * kDecodeWarps * 2 * 16 * D * 2;
+}
+template <int D, int STAGES>
+constexpr size_t decode_smem_bytes() {
+    // pipeline + warp-merge staging [4][8][32] + fo[8][D] + wm/wl[4][8] x2 + fm, fl + flag pad + merge weights
+    // + cumulative tile table
+    return decode_pipe_bytes<D, STAGES>() +
+           (kDecodeWarps * kHeadsPerCta * 32 + kHeadsPerCta * D + 2 * kDecodeWarps * kHeadsPerCta + 2 * kHeadsPerCta + 4 +
+            2 * kDecodeMaxParts * kHeadsPerCta + kHeadsPerCta + (kMaxSeqsPerLaunch + 4)) * sizeof(float);
+}
 
 template <int D, int STAGES>
 __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __grid_constant__ AttnLaunch p) {
@@ -47,223 +78,321 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     constexpr int KS = D / 16;                   // k-steps of the QK^T product
     constexpr int NT = D / 8;                    // n-tiles of the PV product
 
+    float* wpart = reinterpret_cast<float*>(smem + decode_pipe_bytes<D, STAGES>());  // [4][8][32]
+    float* fo = wpart + kDecodeWarps * kHeadsPerCta * 32;                            // [8][D]
+    float* wm = fo + kHeadsPerCta * D;                                               // [4][8]
+    float* wl = wm + kDecodeWarps * kHeadsPerCta;                                    // [4][8]
+    float* fm = wl + kDecodeWarps * kHeadsPerCta;                                    // [8]
+    float* fl = fm + kHeadsPerCta;                                                   // [8]
+    int* flag = reinterpret_cast<int*>(fl + kHeadsPerCta);
+    float* wscratch = fl + kHeadsPerCta + 4;  // [2][kDecodeMaxParts][8] + [8]
+    uint32_t* cum = reinterpret_cast<uint32_t*>(wscratch + 2 * kDecodeMaxParts * kHeadsPerCta + kHeadsPerCta);
+
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t split = blockIdx.x, hy = blockIdx.y, unit = blockIdx.z;
-    const SeqDesc sd = p.seq[unit];
-    const uint32_t kvh = hy / p.gchunks, gc = hy % p.gchunks;
-    const uint32_t head0 = kvh * p.group + gc * kHeadsPerCta;
-    const uint32_t nh = min(static_cast<uint32_t>(kHeadsPerCta), p.group - gc * kHeadsPerCta);
     const uint32_t ring = p.layer.ring;
+    const uint32_t HY = p.layer.kv_heads * p.gchunks;
+    const bool fused = p.k_new != nullptr;
 
-    // This CTA's slice [k0, k1) of the visible keys, in whole tiles.
-    const uint32_t n = sd.kv_hi - sd.kv_lo;
-    uint32_t chunk = (n + p.splits - 1) / p.splits;
-    chunk = (chunk + kTileKeys - 1) / kTileKeys * kTileKeys;
-    const uint32_t k0 = min(n, split * chunk);
-    const uint32_t k1 = min(n, k0 + chunk);
-    const uint32_t span = k1 - k0;
-    const uint32_t ntiles = (span + kTileKeys - 1) / kTileKeys;
-    const uint32_t s0 = (sd.kv_lo + k0) % ring;  // storage row of key k0
-
-    const size_t stream = (static_cast<size_t>(sd.slot) * p.layer.kv_heads + kvh) * ring * D;
-    const __half* kbase = static_cast<const __half*>(p.layer.k) + stream;
-    const __half* vbase = static_cast<const __half*>(p.layer.v) + stream;
-
-    // Query fragments: row g = head g (hi term), row g + 8 = the same head's lo term.
-    uint32_t qa[KS][4];
-    {
-        const float* qrow = p.q + (static_cast<size_t>(unit) * p.q_heads + head0 + g) * D;
-        const bool live = static_cast<uint32_t>(g) < nh;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
-            if (live) {
-                x0 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t);
-                x1 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 8 + 2 * t);
-            }
-            __half h0, l0, h1, l1;
-            split_half(x0.x, h0, l0);
-            split_half(x0.y, h1, l1);
-            qa[ks][0] = pack_half2(h0, h1);
-            qa[ks][1] = pack_half2(l0, l1);
-            split_half(x1.x, h0, l0);
-            split_half(x1.y, h1, l1);
-            qa[ks][2] = pack_half2(h0, h1);
-            qa[ks][3] = pack_half2(l0, l1);
+    // cum[s] = tiles of all cells before sequence s
+    if (tid == 0) {
+        uint32_t c = 0;
+        for (uint32_t s = 0; s < p.n_seqs; ++s) {
+            cum[s] = c;
+            c += (p.seq[s].kv_hi - p.seq[s].kv_lo + kTileKeys - 1) / kTileKeys * HY;
         }
+        cum[p.n_seqs] = c;
     }
+    __syncthreads();
+    const uint32_t total = cum[p.n_seqs];
+    const uint32_t per = p.tiles_per_cta;
+    const uint32_t g0 = blockIdx.x * per;
+    if (g0 >= total) return;
+    const uint32_t ntiles = min(total, g0 + per) - g0;
+
+    auto enter_seq = [&](TileCursor& c) {
+        const SeqDesc sd = p.seq[c.seq];
+        c.n = sd.kv_hi - sd.kv_lo;
+        c.T = (c.n + kTileKeys - 1) / kTileKeys;
+        c.s0 = sd.kv_lo % ring;
+        c.slot = sd.slot;
+    };
+    auto advance = [&](TileCursor& c) {
+        if (++c.tile == c.T) {
+            c.tile = 0;
+            if (++c.hy == HY) {
+                c.hy = 0;
+                if (++c.seq < p.n_seqs) enter_seq(c);
+            }
+        }
+    };
+    TileCursor lc;  // load cursor, runs STAGES - 1 tiles ahead of the compute cursor
+    {
+        uint32_t s = 0;
+        while (s + 1 < p.n_seqs && cum[s + 1] <= g0) ++s;
+        lc.seq = s;
+        enter_seq(lc);
+        const uint32_t r = g0 - cum[s];
+        lc.hy = r / lc.T;
+        lc.tile = r % lc.T;
+    }
+    TileCursor cc = lc;
 
     const uint32_t smem_base = smem_u32(smem);
     auto slice_addr = [&](uint32_t stage, int which) -> uint32_t {
         return smem_base + ((stage * kDecodeWarps + warp) * 2 + which) * kSliceBytes;
     };
-    // Issue this warp's loads for one tile: 16 rows x kRowBytes of K and of V.
-    auto load_tile = [&](uint32_t tile) {
-        const uint32_t stage = tile % STAGES;
+    // Issue this warp's loads for the tile under the load cursor: 16 rows x kRowBytes of K and of V.  Rows past
+    // the sequence's end - and the row the kernel is about to write itself - are zero-filled, not read.
+    auto load_tile = [&](const TileCursor& c, uint32_t stage) {
+        const uint32_t kvh = c.hy / p.gchunks;
+        const size_t stream = (static_cast<size_t>(c.slot) * p.layer.kv_heads + kvh) * ring * D;
+        const __half* kb = static_cast<const __half*>(p.layer.k) + stream;
+        const __half* vb = static_cast<const __half*>(p.layer.v) + stream;
         const uint32_t kbuf = slice_addr(stage, 0), vbuf = slice_addr(stage, 1);
-        const uint32_t row0 = tile * kTileKeys + warp * 16;
+        const uint32_t row0 = c.tile * kTileKeys + warp * 16;
 #pragma unroll
         for (int i = 0; i < D / 16; ++i) {
             const int cid = i * 32 + lane;
-            const int row = cid / kChunksPerRow, c = cid % kChunksPerRow;
-            const uint32_t kr = row0 + row;  // key index relative to k0
-            const bool valid = kr < span;
-            uint32_t srow = s0 + kr;  // span <= ring, so one wrap at most
+            const int row = cid / kChunksPerRow, ch = cid % kChunksPerRow;
+            const uint32_t kr = row0 + row;  // key index inside the sequence's visible range
+            const bool valid = kr < c.n && !(fused && kr == c.n - 1);
+            uint32_t srow = c.s0 + kr;  // n <= ring, so one wrap at most
             if (srow >= ring) srow -= ring;
-            const size_t goff = static_cast<size_t>(valid ? srow : 0u) * D + c * 8;
-            const uint32_t soff = row * kRowBytes + ((c ^ (row & 7)) << 4);
-            cp_async16(kbuf + soff, kbase + goff, valid ? 16u : 0u);
-            cp_async16(vbuf + soff, vbase + goff, valid ? 16u : 0u);
+            const size_t goff = static_cast<size_t>(valid ? srow : 0u) * D + ch * 8;
+            const uint32_t soff = row * kRowBytes + ((ch ^ (row & 7)) << 4);
+            cp_async16(kbuf + soff, kb + goff, valid ? 16u : 0u);
+            cp_async16(vbuf + soff, vb + goff, valid ? 16u : 0u);
         }
     };
 
-    float o[NT][4];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    const float sl = p.scale * kLog2e;
-
+    uint32_t issued = 0;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (static_cast<uint32_t>(s) < ntiles) load_tile(s);
+        if (issued < ntiles) {
+            load_tile(lc, issued % STAGES);
+            advance(lc);
+            ++issued;
+        }
         cp_async_commit();
     }
 
+    uint32_t qa[KS][4];
+    float o[NT][4];
+    float m = -INFINITY, l = 0.f;
+    const float sl = p.scale * kLog2e;
     const int mi = lane >> 3, rr = lane & 7;
-    for (uint32_t tile = 0; tile < ntiles; ++tile) {
-        cp_async_wait<STAGES - 2>();
-        __syncwarp();
-        if (tile + STAGES - 1 < ntiles) load_tile(tile + STAGES - 1);
-        cp_async_commit();
+    bool fresh = true;
+    uint32_t head0 = 0, nh = 0, kvh = 0, gc = 0;
 
-        const uint32_t row0 = tile * kTileKeys + warp * 16;
-        if (row0 >= span) continue;  // this warp's slice is past the end (last tile only)
-        const uint32_t stage = tile % STAGES;
-        const uint32_t kbuf = slice_addr(stage, 0), vbuf = slice_addr(stage, 1);
-
-        // S(16 x 16 keys) = Q(16 x D) * K^T
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        {
-            const int krow = ((mi >> 1) << 3) + rr;
-            const uint32_t rbase = kbuf + krow * kRowBytes;
+    for (uint32_t i = 0; i < ntiles; ++i) {
+        if (fresh) {
+            // Entering a cell: its query fragments (row g = head g's hi term, row g + 8 = its lo term) and a
+            // clean softmax state.
+            kvh = cc.hy / p.gchunks;
+            gc = cc.hy % p.gchunks;
+            head0 = kvh * p.group + gc * kHeadsPerCta;
+            nh = min(static_cast<uint32_t>(kHeadsPerCta), p.group - gc * kHeadsPerCta);
+            const float* qrow = p.q + (static_cast<size_t>(cc.seq) * p.q_heads + head0 + g) * D;
+            const bool live = static_cast<uint32_t>(g) < nh;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
-                uint32_t b[4];
-                ldmatrix_x4(b, rbase + (((2 * ks + (mi & 1)) ^ rr) << 4));
-                mma_16816(s[0], qa[ks], b[0], b[1]);
-                mma_16816(s[1], qa[ks], b[2], b[3]);
+                float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
+                if (live) {
+                    x0 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t);
+                    x1 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 8 + 2 * t);
+                }
+                __half h0, l0, h1, l1;
+                split_half(x0.x, h0, l0);
+                split_half(x0.y, h1, l1);
+                qa[ks][0] = pack_half2(h0, h1);
+                qa[ks][1] = pack_half2(l0, l1);
+                split_half(x1.x, h0, l0);
+                split_half(x1.y, h1, l1);
+                qa[ks][2] = pack_half2(h0, h1);
+                qa[ks][3] = pack_half2(l0, l1);
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+            m = -INFINITY;
+            l = 0.f;
+            fresh = false;
+        }
+        cp_async_wait<STAGES - 2>();
+        __syncwarp();
+        if (issued < ntiles) {
+            load_tile(lc, issued % STAGES);
+            advance(lc);
+            ++issued;
+        }
+        cp_async_commit();
+
+        const uint32_t row0 = cc.tile * kTileKeys + warp * 16;
+        if (row0 < cc.n) {  // else this warp's slice is past the sequence's end (last tile only)
+            const uint32_t stage = i % STAGES;
+            const uint32_t kbuf = slice_addr(stage, 0), vbuf = slice_addr(stage, 1);
+
+            if (fused && cc.n - 1 >= row0 && cc.n - 1 < row0 + 16) {
+                // This slice holds the step's new position: cast the f32 row, keep it in the cache and put it
+                // where the zero-filled row sits in the staged tile.  Lanes 0..15 take K chunks, 16..31 V chunks.
+                const uint32_t row = cc.n - 1 - row0;
+                const int ch = lane & 15;
+                const bool is_v = lane >= 16;
+                if (ch < kChunksPerRow) {
+                    const float* src = (is_v ? p.v_new : p.k_new) +
+                                       (static_cast<size_t>(cc.seq) * p.layer.kv_heads + kvh) * D + ch * 8;
+                    const uint4 packed = pack8(*reinterpret_cast<const float4*>(src),
+                                               *reinterpret_cast<const float4*>(src + 4));
+                    const uint32_t soff = row * kRowBytes + ((ch ^ (row & 7)) << 4);
+                    *reinterpret_cast<uint4*>(smem + ((is_v ? vbuf : kbuf) - smem_base) + soff) = packed;
+                    if (gc == 0) {
+                        uint32_t srow = cc.s0 + cc.n - 1;
+                        if (srow >= ring) srow -= ring;
+                        const size_t stream = (static_cast<size_t>(cc.slot) * p.layer.kv_heads + kvh) * ring * D;
+                        __half* dst = static_cast<__half*>(const_cast<void*>(is_v ? p.layer.v : p.layer.k)) + stream +
+                                      static_cast<size_t>(srow) * D + ch * 8;
+                        *reinterpret_cast<uint4*>(dst) = packed;
+                    }
+                }
+                __syncwarp();
+            }
+
+            // S(16 x 16 keys) = Q(16 x D) * K^T
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            {
+                const int krow = ((mi >> 1) << 3) + rr;
+                const uint32_t rbase = kbuf + krow * kRowBytes;
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, rbase + (((2 * ks + (mi & 1)) ^ rr) << 4));
+                    mma_16816(s[0], qa[ks], b[0], b[1]);
+                    mma_16816(s[1], qa[ks], b[2], b[3]);
+                }
+            }
+            // hi + lo, scale, mask the tail, online softmax for head g.
+            float sc[2][2];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t kr = row0 + 8 * j + 2 * t + e;
+                    float v = (s[j][e] + s[j][e + 2]) * sl;
+                    v = kr < cc.n ? v : -INFINITY;
+                    sc[j][e] = v;
+                    mx = fmaxf(mx, v);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m, mx);  // finite: key row0 is valid
+            const float corr = fast_exp2(m - m_new);
+            m = m_new;
+            uint32_t pa[4];
+            float psum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float p0 = fast_exp2(sc[j][0] - m_new), p1 = fast_exp2(sc[j][1] - m_new);
+                psum += p0 + p1;
+                __half h0, l0, h1, l1;
+                split_half(p0, h0, l0);
+                split_half(p1, h1, l1);
+                pa[2 * j] = pack_half2(h0, h1);
+                pa[2 * j + 1] = pack_half2(l0, l1);
+            }
+            l = l * corr + psum;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                o[j][0] *= corr;
+                o[j][1] *= corr;
+                o[j][2] *= corr;
+                o[j][3] *= corr;
+            }
+            // O(16 x D) += P(16 x 16 keys) * V(16 keys x D)
+            {
+                const int vrow = ((mi & 1) << 3) + rr;
+                const uint32_t rbase = vbuf + vrow * kRowBytes;
+#pragma unroll
+                for (int jp = 0; jp < NT / 2; ++jp) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, rbase + (((2 * jp + (mi >> 1)) ^ rr) << 4));
+                    mma_16816(o[2 * jp], pa, b[0], b[1]);
+                    mma_16816(o[2 * jp + 1], pa, b[2], b[3]);
+                }
             }
         }
-        // hi + lo, scale, mask the tail, online softmax for head g.
-        float sc[2][2];
-        float mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const uint32_t kr = row0 + 8 * j + 2 * t + e;
-                float v = (s[j][e] + s[j][e + 2]) * sl;
-                v = kr < span ? v : -INFINITY;
-                sc[j][e] = v;
-                mx = fmaxf(mx, v);
+
+        if (cc.tile + 1 == cc.T || i + 1 == ntiles) {
+            // This CTA's part of the cell is complete: merge the 4 warps through shared memory, 32 channels at
+            // a time, then hand the (m, l, o) part to the cell's merge.
+            float lq = l + __shfl_xor_sync(0xffffffffu, l, 1);
+            lq += __shfl_xor_sync(0xffffffffu, lq, 2);
+            __syncthreads();  // the previous cell's epilogue is over for every thread
+            if (t == 0) {
+                wm[warp * kHeadsPerCta + g] = m;
+                wl[warp * kHeadsPerCta + g] = lq;
             }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m, mx);  // finite: key row0 is valid
-        const float corr = fast_exp2(m - m_new);
-        m = m_new;
-        uint32_t pa[4];
-        float psum = 0.f;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const float p0 = fast_exp2(sc[j][0] - m_new), p1 = fast_exp2(sc[j][1] - m_new);
-            psum += p0 + p1;
-            __half h0, l0, h1, l1;
-            split_half(p0, h0, l0);
-            split_half(p1, h1, l1);
-            pa[2 * j] = pack_half2(h0, h1);
-            pa[2 * j + 1] = pack_half2(l0, l1);
-        }
-        l = l * corr + psum;
+            for (int ps = 0; ps < D / 32; ++ps) {
+                float* dst = wpart + (warp * kHeadsPerCta + g) * 32;
 #pragma unroll
-        for (int i = 0; i < NT; ++i) {
-            o[i][0] *= corr;
-            o[i][1] *= corr;
-            o[i][2] *= corr;
-            o[i][3] *= corr;
-        }
-        // O(16 x D) += P(16 x 16 keys) * V(16 keys x D)
-        {
-            const int vrow = ((mi & 1) << 3) + rr;
-            const uint32_t rbase = vbuf + vrow * kRowBytes;
+                for (int j = 0; j < 4; ++j) {
+                    const int nt = 4 * ps + j;
+                    *reinterpret_cast<float2*>(dst + 8 * j + 2 * t) =
+                        make_float2(o[nt][0] + o[nt][2], o[nt][1] + o[nt][3]);
+                }
+                __syncthreads();
+                for (int idx = tid; idx < kHeadsPerCta * 32; idx += kDecodeThreads) {
+                    const int h = idx >> 5, c = idx & 31;
+                    float M = -INFINITY;
 #pragma unroll
-            for (int jp = 0; jp < NT / 2; ++jp) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, rbase + (((2 * jp + (mi >> 1)) ^ rr) << 4));
-                mma_16816(o[2 * jp], pa, b[0], b[1]);
-                mma_16816(o[2 * jp + 1], pa, b[2], b[3]);
+                    for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, wm[w * kHeadsPerCta + h]);
+                    float O = 0.f;
+                    if (M != -INFINITY) {
+#pragma unroll
+                        for (int w = 0; w < kDecodeWarps; ++w) {
+                            const float mw = wm[w * kHeadsPerCta + h];
+                            const float a = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                            O += a * wpart[(w * kHeadsPerCta + h) * 32 + c];
+                        }
+                    }
+                    fo[h * D + 32 * ps + c] = O;
+                }
+                __syncthreads();
             }
+            if (tid < kHeadsPerCta) {
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, wm[w * kHeadsPerCta + tid]);
+                float L = 0.f;
+                if (M != -INFINITY) {
+#pragma unroll
+                    for (int w = 0; w < kDecodeWarps; ++w) {
+                        const float mw = wm[w * kHeadsPerCta + tid];
+                        L += ((mw == -INFINITY) ? 0.f : fast_exp2(mw - M)) * wl[w * kHeadsPerCta + tid];
+                    }
+                }
+                fm[tid] = M;
+                fl[tid] = L;
+            }
+            __syncthreads();
+            // which CTAs share this cell, and which of them this one is
+            const uint32_t gs = cum[cc.seq] + cc.hy * cc.T;
+            const uint32_t first = gs / per, last = (gs + cc.T - 1) / per;
+            finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, last - first + 1, blockIdx.x - first, head0,
+                                                         nh, D, fo, fm, fl, flag, wscratch);
+            fresh = true;
         }
+        advance(cc);
     }
     cp_async_wait<0>();
-    __syncthreads();  // every warp is done with its pipeline buffers
-
-    // Per-warp results into shared memory, then one merge across the 4 warps.
-    float* wo = reinterpret_cast<float*>(smem);                       // [4][8][D]
-    float* wm = wo + kDecodeWarps * kHeadsPerCta * D;                 // [4][8]
-    float* wl = wm + kDecodeWarps * kHeadsPerCta;                     // [4][8]
-    float* fo = wl + kDecodeWarps * kHeadsPerCta;                     // [8][D]
-    float* fm = fo + kHeadsPerCta * D;                                // [8]
-    float* fl = fm + kHeadsPerCta;                                    // [8]
-    int* flag = reinterpret_cast<int*>(fl + kHeadsPerCta);
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    {
-        float* dst = wo + (warp * kHeadsPerCta + g) * D;
-#pragma unroll
-        for (int i = 0; i < NT; ++i) {
-            float2 v = make_float2(o[i][0] + o[i][2], o[i][1] + o[i][3]);
-            *reinterpret_cast<float2*>(dst + 8 * i + 2 * t) = v;
-        }
-        if (t == 0) {
-            wm[warp * kHeadsPerCta + g] = m;
-            wl[warp * kHeadsPerCta + g] = l;
-        }
-    }
-    __syncthreads();
-    for (int idx = tid; idx < kHeadsPerCta * D; idx += kDecodeThreads) {
-        const int h = idx / D;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, wm[w * kHeadsPerCta + h]);
-        float O = 0.f, L = 0.f;
-        if (M != -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < kDecodeWarps; ++w) {
-                const float mw = wm[w * kHeadsPerCta + h];
-                const float a = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-                O += a * wo[(w * kHeadsPerCta + h) * D + (idx % D)];
-                L += a * wl[w * kHeadsPerCta + h];
-            }
-        }
-        fo[idx] = O;
-        if ((idx % D) == 0) {
-            fm[h] = M;
-            fl[h] = L;
-        }
-    }
-    __syncthreads();
-    finish_unit<kDecodeThreads>(p, unit, hy, split, head0, nh, D, fo, fm, fl, flag);
 }
 
-template <int D, int STAGES>
-constexpr size_t decode_smem_bytes() {
-    return static_cast<size_t>(STAGES) * kDecodeWarps * 2 * 16 * D * 2;
-}
+constexpr int kStages128 = 3;  // 96 KiB of pipeline per CTA at D = 128, two CTAs per SM
+constexpr int kStages64 = 4;   // 64 KiB at D = 64
 
-constexpr int kStages128 = 3;  // 96 KiB per CTA at D = 128, two CTAs per SM
-constexpr int kStages64 = 4;   // 64 KiB per CTA at D = 64
+// Most CTAs that can share a cell of T tiles when every CTA walks `per` tiles.
+uint32_t parts_for(uint32_t T, uint32_t per) { return (T + per - 2) / per + 1; }
 
 }  // namespace
 
@@ -280,11 +409,33 @@ cudaError_t configure_decode_f16() {
                                 static_cast<int>(decode_smem_bytes<64, kStages64>()));
 }
 
-cudaError_t launch_decode_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches) {
-    const dim3 grid(p.splits, p.layer.kv_heads * p.gchunks, p.n_seqs);
+cudaError_t launch_decode_f16(AttnLaunch p, uint32_t cta_slots, uint32_t max_parts, cudaStream_t s,
+                              uint64_t* launches, uint32_t* parts_used) {
+    if (p.n_seqs == 0 || p.n_seqs > static_cast<uint32_t>(kMaxSeqsPerLaunch) || p.rows != 1) return cudaErrorInvalidValue;
+    const uint32_t HY = p.layer.kv_heads * p.gchunks;
+    uint64_t total = 0;
+    uint32_t tmax = 0;
+    for (uint32_t i = 0; i < p.n_seqs; ++i) {
+        const uint32_t n = p.seq[i].kv_hi - p.seq[i].kv_lo;
+        if (n == 0 || n > p.layer.ring) return cudaErrorInvalidValue;
+        const uint32_t T = (n + kTileKeys - 1) / kTileKeys;
+        total += static_cast<uint64_t>(T) * HY;
+        if (T > tmax) tmax = T;
+    }
+    if (total == 0 || total > 0xffffffffull) return cudaErrorInvalidValue;
+    if (max_parts > kDecodeMaxParts) max_parts = kDecodeMaxParts;
+    if (max_parts < 2) max_parts = 2;
+    if (cta_slots == 0) cta_slots = 1;
+    uint64_t ctas = total < cta_slots ? total : cta_slots;
+    uint32_t per = static_cast<uint32_t>((total + ctas - 1) / ctas);
+    while (parts_for(tmax, per) > max_parts) ++per;  // fewer, longer runs when the scratch bounds the sharing
+    ctas = (total + per - 1) / per;
+    p.tiles_per_cta = per;
+    p.splits = parts_for(tmax, per);
+    if (parts_used) *parts_used = p.splits;
+    const dim3 grid(static_cast<unsigned int>(ctas));
     if (p.layer.head_dim == 128) {
-        decode_f16_kernel<128, kStages128>
-            <<<grid, kDecodeThreads, decode_smem_bytes<128, kStages128>(), s>>>(p);
+        decode_f16_kernel<128, kStages128><<<grid, kDecodeThreads, decode_smem_bytes<128, kStages128>(), s>>>(p);
     } else if (p.layer.head_dim == 64) {
         decode_f16_kernel<64, kStages64><<<grid, kDecodeThreads, decode_smem_bytes<64, kStages64>(), s>>>(p);
     } else {
@@ -315,8 +466,10 @@ cudaError_t launch_decode_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* lau
 //    library, from load until the process exits, whether or not this entry
 //    point is ever used;
 //  - (sequences x KV heads x head chunks) x splits may not exceed
-//    kNoAllocCellSplits, sequences may not exceed 64, head_dim is 64 or 128;
-//    anything larger is refused with ITK_ERR_CAPACITY and a message;
+//    kNoAllocCellSplits, where `splits` bounds how many CTAs may share one
+//    (sequence, head) key range (at least 2 are always reserved); sequences may
+//    not exceed 64, head_dim is 64 or 128; anything larger is refused with
+//    ITK_ERR_CAPACITY and a message;
 //  - all calls share the one array and it keeps whatever the previous call
 //    left.  The arrival counters are the only part that must read zero at
 //    launch; every call clears them on its stream first.  Two calls whose
@@ -389,22 +542,25 @@ extern "C" int itk_decode_attention_noalloc(const void* k_layer, const void* v_l
         return noalloc_refuse(102, error_text, error_text_len,
                               "%llu (sequence, head) cells exceed the built-in scratch of %llu", cells,
                               static_cast<unsigned long long>(kNoAllocCellSplits));
-    if (splits == 0) {  // a few hundred CTAs, at least four 64-key tiles each
-        unsigned long long s = (296 * 2 + cells - 1) / cells;
-        const unsigned long long by_len = (n_max + 255) / 256;
-        if (s > by_len) s = by_len;
-        if (s * cells > kNoAllocCellSplits) s = kNoAllocCellSplits / cells;
-        splits = static_cast<uint32_t>(s < 1 ? 1 : s);
-    }
-    if (cells * splits > kNoAllocCellSplits)
+    if (splits > static_cast<uint32_t>(kMaxSplits))
+        return noalloc_refuse(102, error_text, error_text_len, "%llu splits exceed the kernel's maximum of %llu", splits,
+                              static_cast<unsigned long long>(kMaxSplits));
+    // `splits` bounds the CTAs that may share one key range, i.e. the partial slots a cell needs.
+    unsigned long long parts = splits == 0 ? kNoAllocCellSplits / cells : (splits < 2 ? 2 : splits);
+    if (parts > kDecodeMaxParts) parts = kDecodeMaxParts;
+    if (parts < 2 || cells * parts > kNoAllocCellSplits)
         return noalloc_refuse(102, error_text, error_text_len,
-                              "cells x splits = %llu exceeds the built-in scratch of %llu partial slots; lower `splits`",
-                              cells * splits, static_cast<unsigned long long>(kNoAllocCellSplits));
+                              "cells x splits = %llu exceeds the built-in scratch of %llu partial slots; lower `splits` "
+                              "or pass fewer sequences",
+                              cells * (parts < 2 ? 2 : parts), static_cast<unsigned long long>(kNoAllocCellSplits));
 
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices)
         return noalloc_refuse(100, error_text, error_text_len, "no usable current CUDA device");
+    int sm_count = 0;
+    e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || sm_count <= 0) sm_count = 148;
     if (!g_noalloc_ptr[dev]) {
         // One-time set-up for this device: resolve the array's device address and opt the kernel in to its
         // dynamic shared memory size.  Neither allocates.
@@ -443,13 +599,13 @@ extern "C" int itk_decode_attention_noalloc(const void* k_layer, const void* v_l
     p.gchunks = gchunks;
     p.rows = 1;
     p.n_seqs = n_seqs;
-    p.splits = splits;
     p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
     for (uint32_t i = 0; i < n_seqs; ++i) p.seq[i] = SeqDesc{slots[i], kv_len[i] - 1, 0, kv_len[i]};
     // The arrival counters must read zero when the kernel starts, whatever an earlier (possibly failed)
     // call left behind.
     e = cudaMemsetAsync(p.tickets, 0, cells * sizeof(unsigned int), stream);
-    if (e == cudaSuccess) e = launch_decode_f16(p, stream, nullptr);
+    if (e == cudaSuccess)
+        e = launch_decode_f16(p, 2u * static_cast<uint32_t>(sm_count), static_cast<uint32_t>(parts), stream, nullptr, nullptr);
     if (e != cudaSuccess) {
         if (error_text && error_text_len)
             snprintf(error_text, error_text_len, "decode attention launch failed: %s", cudaGetErrorString(e));

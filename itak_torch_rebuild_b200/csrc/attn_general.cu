@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(kGenThreads) attn_general_kernel(const __grid_
     float* l_s = m_s + kHeadsPerCta;                      // [8]
     float* corr = l_s + kHeadsPerCta;                     // [8]
     int* flag = reinterpret_cast<int*>(corr + kHeadsPerCta);
+    float* wscratch = corr + kHeadsPerCta + 4;            // merge weights: [2][256][8] + [8]
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t split = blockIdx.x, hy = blockIdx.y, unit = blockIdx.z;
@@ -153,18 +154,19 @@ __global__ void __launch_bounds__(kGenThreads) attn_general_kernel(const __grid_
         if (idx < nh * D) fo[idx] = o[i];
     }
     __syncthreads();
-    finish_unit<kGenThreads>(p, unit, hy, split, head0, nh, D, fo, m_s, l_s, flag);
+    finish_unit<kGenThreads, kMaxSplits>(p, unit, hy, p.splits, split, head0, nh, D, fo, m_s, l_s, flag, wscratch);
 }
 
 size_t general_smem_bytes(uint32_t D) {
-    return (static_cast<size_t>(kHeadsPerCta) * D * 2 + kHeadsPerCta * kGenTile + 3 * kHeadsPerCta) * sizeof(float) +
-           16;
+    return (static_cast<size_t>(kHeadsPerCta) * D * 2 + kHeadsPerCta * kGenTile + 3 * kHeadsPerCta + 4 +
+            2 * kMaxSplits * kHeadsPerCta + kHeadsPerCta) * sizeof(float);
 }
 
 }  // namespace
 
 cudaError_t launch_attn_general(const AttnLaunch& p, bool f16, cudaStream_t s, uint64_t* launches) {
     if (p.layer.head_dim == 0 || p.layer.head_dim > kGenMaxD) return cudaErrorInvalidValue;
+    if (p.splits == 0 || p.splits > static_cast<uint32_t>(kMaxSplits)) return cudaErrorInvalidValue;
     const dim3 grid(p.splits, p.layer.kv_heads * p.gchunks, p.n_seqs * p.rows);
     const size_t smem = general_smem_bytes(p.layer.head_dim);
     if (f16)

@@ -89,6 +89,8 @@ struct itk_backend {
     itk_stats stats{};
     int sm_count = 148;
     int forced_splits = 0;
+    int forced_ctas = 0;         // ITK_DECODE_CTAS: persistent CTAs of the decode kernel (default 2 per SM)
+    bool separate_append = false;  // ITK_SEPARATE_APPEND=1: decode steps launch the append kernel separately
     bool force_general = false;  // ITK_FORCE_GENERAL=1: multi-row launches take the CUDA-core kernel (A/B checks)
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
     std::vector<cudaEvent_t> prof_events;
@@ -140,6 +142,7 @@ uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uin
         const uint64_t by_len = (n_max + tile - 1) / tile;
         if (s > by_len) s = by_len;
         if (s * cells * scratch_mult > kPartCellSplits) s = kPartCellSplits / (cells * scratch_mult);
+        if (s > 256) s = 256;
         return static_cast<uint32_t>(s < 1 ? 1 : s);
     }
     const uint64_t slots = static_cast<uint64_t>(b->sm_count) * 2;
@@ -211,8 +214,10 @@ int run_append(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, 
 }
 
 // Launch attention for `n` sequences of `rows` rows each (device q / out).
+// `d_k_new` / `d_v_new` (device f32 [n][kv_heads*D], may be null): the step's new rows for the decode kernel to
+// store itself; only honoured when the decode kernel takes the launch (see decode_fuses_append).
 int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, uint32_t rows, const float* d_q,
-                  float* d_out) {
+                  float* d_out, const float* d_k_new = nullptr, const float* d_v_new = nullptr) {
     const uint32_t D = b->cfg.head_dim;
     const uint32_t HY = b->cfg.kv_heads * b->gchunks;
     const bool decode = b->f16 && itk::decode_f16_supported(D, rows);
@@ -252,13 +257,28 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
         if (cells > b->ticket_cells)
             return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(cells) + " (row, head) cells exceed the scratch of " +
                                                  zu(b->ticket_cells));
-        p.splits = choose_splits(b, cells, n_max, (decode || verify) ? 64 : 128, verify ? 4 : 1);
-        b->stats.last_splits = p.splits;
         b->stats.kv_bytes_read += keys * b->cfg.kv_heads * D * 2ull * b->elem_bytes;
         const long ev = prof_begin(b, 0);
-        if (decode)
-            ITK_CUDA(b, itk::launch_decode_f16(p, b->stream, &b->stats.kernel_launches), "decode attention launch");
-        else if (verify)
+        if (decode) {
+            if (d_k_new) {
+                p.k_new = d_k_new + static_cast<size_t>(at) * b->row_len();
+                p.v_new = d_v_new + static_cast<size_t>(at) * b->row_len();
+            }
+            uint64_t max_parts = kPartCellSplits / cells;
+            if (max_parts > itk::kDecodeMaxParts) max_parts = itk::kDecodeMaxParts;
+            const uint32_t ctas = b->forced_ctas > 0 ? static_cast<uint32_t>(b->forced_ctas)
+                                                     : 2u * static_cast<uint32_t>(b->sm_count);
+            uint32_t parts = 0;
+            ITK_CUDA(b, itk::launch_decode_f16(p, ctas, static_cast<uint32_t>(max_parts), b->stream,
+                                               &b->stats.kernel_launches, &parts),
+                     "decode attention launch");
+            b->stats.last_splits = parts;
+            prof_end(b, ev);
+            continue;
+        }
+        p.splits = choose_splits(b, cells, n_max, verify ? 64 : 128, verify ? 4 : 1);
+        b->stats.last_splits = p.splits;
+        if (verify)
             ITK_CUDA(b, itk::launch_verify_f16(p, b->stream, &b->stats.kernel_launches), "verify attention launch");
         else
             ITK_CUDA(b, itk::launch_attn_general(p, b->f16, b->stream, &b->stats.kernel_launches),
@@ -266,6 +286,12 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
         prof_end(b, ev);
     }
     return ITK_OK;
+}
+
+// A decode step (one row per sequence, f16 cache, head_dim 64 or 128) lets the attention kernel store the new
+// row itself; ITK_SEPARATE_APPEND=1 keeps the two-launch form for A/B checks.
+bool decode_fuses_append(const itk_backend* b, uint32_t rows) {
+    return b->f16 && !b->separate_append && (b->cfg.head_dim % 8 == 0) && itk::decode_f16_supported(b->cfg.head_dim, rows);
 }
 
 // Shared validation of one attention step; fills `seqs`.  Mirrors
@@ -324,7 +350,9 @@ int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t*
                 uint32_t rows, const float* d_q, const float* d_k, const float* d_v, float* d_out) {
     std::vector<SeqDesc> seqs;
     if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
-    if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
+    const bool fuse = decode_fuses_append(b, rows);
+    if (!fuse)
+        if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
     for (uint32_t i = 0; i < n_seqs; ++i) {
         SlotState& st = b->slots[slots[i]];
         st.appended[layer] += rows;
@@ -332,7 +360,7 @@ int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t*
     }
     b->stats.rows_appended += static_cast<uint64_t>(n_seqs) * rows;
     b->stats.attention_calls += 1;
-    return run_attention(b, layer, n_seqs, seqs.data(), rows, d_q, d_out);
+    return run_attention(b, layer, n_seqs, seqs.data(), rows, d_q, d_out, fuse ? d_k : nullptr, fuse ? d_v : nullptr);
 }
 
 int ensure_gather(itk_backend* b, size_t bytes) {
@@ -504,6 +532,8 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     b->slots.resize(cfg->n_slots);
     for (uint32_t s = 0; s < cfg->n_slots; ++s) drop_slot(b, s);
     if (const char* env = std::getenv("ITK_DECODE_SPLITS")) b->forced_splits = std::atoi(env);
+    if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
+    if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     *out = b;
     return ITK_OK;

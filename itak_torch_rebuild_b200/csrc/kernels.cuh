@@ -55,7 +55,11 @@ struct AttnLaunch {
     uint32_t gchunks;        // ceil(group / 8): head chunks per kv head
     uint32_t rows;           // query rows per sequence
     uint32_t n_seqs;
-    uint32_t splits;         // CTAs along the key range
+    uint32_t splits;         // partial slots per cell in the scratch: the CTAs along a key range (general and
+                             // verify kernels) or the most CTAs that can share one cell (decode kernel)
+    uint32_t tiles_per_cta;  // decode kernel: 64-key tiles each persistent CTA walks
+    const float* k_new;      // decode kernel: when set, the step's new K rows [n_seqs][kv_heads][D] (f32); the
+    const float* v_new;      // kernel stores them at position kv_hi - 1 itself instead of a separate append
     float scale;             // score scale, 1/sqrt(D) by default
     SeqDesc seq[kMaxSeqsPerLaunch];
 };
@@ -99,8 +103,13 @@ struct CopyLaunch {
 cudaError_t launch_append(const AppendLaunch& p, bool f16, cudaStream_t s, uint64_t* launches);
 // f32 -> cache element type, flat (used to import f32 snapshot rows).
 cudaError_t launch_convert(const float* src, void* dst, size_t n, bool f16, cudaStream_t s, uint64_t* launches);
-// Flash-decode over an f16 cache, rows == 1, head_dim 64 or 128 (tensor-core path).
-cudaError_t launch_decode_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);
+// Flash-decode over an f16 cache, rows == 1, head_dim 64 or 128 (tensor-core path).  `p` carries everything
+// but the work partition, which the launcher derives for `cta_slots` resident CTAs; at most `max_parts` CTAs
+// may share one (sequence, head) cell (bounds the scratch: cells * max_parts partial slots).  The number of
+// partial slots per cell actually used is returned through *parts_used.
+cudaError_t launch_decode_f16(AttnLaunch p, uint32_t cta_slots, uint32_t max_parts, cudaStream_t s,
+                              uint64_t* launches, uint32_t* parts_used);
+constexpr uint32_t kDecodeMaxParts = 64;
 bool decode_f16_supported(uint32_t head_dim, uint32_t rows);
 // Multi-row causal attention over an f16 cache (chunked prefill / speculative verify).
 cudaError_t launch_verify_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);

@@ -5,29 +5,11 @@
 // are bit-exact by contract.  Bound: HBM (read + write of the moved bytes);
 // an append of a few rows is launch latency.
 #include "kernels.cuh"
+#include "kv_convert.cuh"
 
 namespace itk {
 
 namespace {
-
-// IEEE round-to-nearest-even f32 -> f16 with the reference's NaN rule: every
-// NaN becomes sign | 0x7e00 (crates/wgpu-compute/src/kernels/k1_q4k_gemv.rs:285-329).
-// The hardware conversion already gives RNE for normals and subnormals,
-// overflow to infinity and signed zero on underflow; only its NaN payload differs.
-__device__ __forceinline__ unsigned short f32_to_f16_bits(float x) {
-    const unsigned short h = __half_as_ushort(__float2half_rn(x));
-    if (x != x) return static_cast<unsigned short>(((__float_as_uint(x) >> 16) & 0x8000u) | 0x7e00u);
-    return h;
-}
-
-__device__ __forceinline__ uint4 pack8(const float4& a, const float4& b) {
-    uint4 r;
-    r.x = f32_to_f16_bits(a.x) | (static_cast<uint32_t>(f32_to_f16_bits(a.y)) << 16);
-    r.y = f32_to_f16_bits(a.z) | (static_cast<uint32_t>(f32_to_f16_bits(a.w)) << 16);
-    r.z = f32_to_f16_bits(b.x) | (static_cast<uint32_t>(f32_to_f16_bits(b.y)) << 16);
-    r.w = f32_to_f16_bits(b.z) | (static_cast<uint32_t>(f32_to_f16_bits(b.w)) << 16);
-    return r;
-}
 
 // Stores VEC consecutive elements starting at element offset `off`.
 template <bool F16, int VEC>

@@ -10,7 +10,7 @@ import pytest
 from itak_torch_rebuild_b200 import CudaCompute, CudaComputeError, KvDtype, PositionCache, _lib
 from oracle import oracle as orc
 
-from kvparity import assert_attention_close, make_pair, stored
+from kvparity import assert_attention_close, assert_view_equal, make_pair, stored
 
 pytestmark = pytest.mark.gpu
 
@@ -70,14 +70,19 @@ def test_attention_validation_is_named_errors():
     assert e.value.code == _lib.ERR_NON_DIVISIBLE_HEADS
 
 
-def seeded_case(dtype, hq, hkv, d, n, seed, layer_window=(0,), splits=None):
-    """Append n seeded N(0,1) rows, then one decode step through the backend's attention call."""
-    if splits is not None:
-        os.environ["ITK_DECODE_SPLITS"] = str(splits)
+def seeded_case(dtype, hq, hkv, d, n, seed, layer_window=(0,), ctas=None, separate_append=False):
+    """Append n seeded N(0,1) rows, then decode steps through the backend's attention call; the outputs and,
+    afterwards, the cache contents (the step's rows are stored by the attention launch itself on the f16
+    tensor-core path) are compared with the oracle."""
+    if ctas is not None:
+        os.environ["ITK_DECODE_CTAS"] = str(ctas)
+    if separate_append:
+        os.environ["ITK_SEPARATE_APPEND"] = "1"
     try:
         gpu, (ref,) = make_pair(list(layer_window), hq, hkv, d, dtype=dtype, max_context=n + 8, chunk_cap=1)
     finally:
-        os.environ.pop("ITK_DECODE_SPLITS", None)
+        os.environ.pop("ITK_DECODE_CTAS", None)
+        os.environ.pop("ITK_SEPARATE_APPEND", None)
     rng = np.random.default_rng(seed)
     worst = 0.0
     for layer in range(len(layer_window)):
@@ -87,7 +92,7 @@ def seeded_case(dtype, hq, hkv, d, n, seed, layer_window=(0,), splits=None):
         ref.append_rows(layer, stored(k, dtype), stored(v, dtype), 0)
     pos = PositionCache()
     pos.advance(n)
-    for step in range(2):
+    for step in range(3):
         for layer in range(len(layer_window)):
             q = rng.standard_normal(hq * d).astype(np.float32)
             kn = rng.standard_normal(hkv * d).astype(np.float32)
@@ -97,6 +102,8 @@ def seeded_case(dtype, hq, hkv, d, n, seed, layer_window=(0,), splits=None):
             want = orc.gqa_attention(q, 1, hq, [pos.position()], ref.view(layer))
             worst = max(worst, assert_attention_close(got, want, hq, d, dtype, f"n={n} step={step} layer={layer}"))
         pos.advance(1)
+    for layer in range(len(layer_window)):
+        assert_view_equal(gpu, ref, layer, dtype)
     return worst, gpu.stats()
 
 
@@ -107,12 +114,22 @@ def test_f16_decode_kernel_every_tail_length(n, d):
     seeded_case(KvDtype.F16, 8, 2, d, n, seed=n * 7 + d)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8, 16, 33])
-def test_f16_decode_kernel_every_split_count(splits):
-    """The split-K merge (last CTA combines): every split count gives the single-CTA answer to tolerance,
-    including splits that leave some CTAs with an empty key range."""
-    _, st = seeded_case(KvDtype.F16, 8, 2, 128, 700, seed=11, splits=splits)
-    assert st["last_splits"] == min(splits, (702 + 63) // 64)
+@pytest.mark.parametrize("ctas", [1, 2, 3, 5, 8, 16, 33, 97, 296])
+def test_f16_decode_kernel_every_partition(ctas):
+    """The persistent partition and the merge (last CTA combines): any number of CTAs gives the same answer to
+    tolerance - one CTA walking every cell in turn, CTAs whose run crosses a cell boundary, and more CTAs
+    than tiles."""
+    _, st = seeded_case(KvDtype.F16, 8, 2, 128, 700, seed=11, ctas=ctas)
+    assert 1 <= st["last_splits"] <= 64
+
+
+def test_f16_decode_fused_append_equals_the_separate_append():
+    """The decode launch that stores the step's new row itself leaves the same cache bits and the same outputs
+    as the two-launch form (append kernel, then attention)."""
+    a, sa = seeded_case(KvDtype.F16, 32, 8, 128, 515, seed=5)
+    b, sb = seeded_case(KvDtype.F16, 32, 8, 128, 515, seed=5, separate_append=True)
+    assert sb["kernel_launches"] == sa["kernel_launches"] + 3
+    assert abs(a - b) < 1e-6
 
 
 @pytest.mark.parametrize("hq,hkv", [(1, 1), (2, 1), (4, 1), (8, 1), (16, 1), (32, 8), (64, 8), (32, 2), (12, 4)])
@@ -151,6 +168,9 @@ def test_sliding_layers_mask_and_wrap(dtype):
             want = orc.gqa_attention(q, 1, hq, [step], ref.view(layer))
             assert_attention_close(got, want, hq, d, dtype, f"step {step} layer {layer}")
         pos.advance(1)
+        if step % 40 == 39:
+            for layer in range(2):
+                assert_view_equal(gpu, ref, layer, dtype)
 
 
 # crates/wgpu-compute/tests/fused_kernels.rs:506-624: the seven geometries of the flash-vs-two-pass test,
