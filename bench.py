@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--workload", default="c5_long_context_decode", choices=sorted(WORKLOADS))
     ap.add_argument("--context", type=int, default=None, help="override the context length (smoke runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (smoke runs)")
+    ap.add_argument("--no-graph", action="store_true", help="launch every layer directly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-units", type=int, default=None, help="(sequence, layer) units in the CPU sample")
@@ -230,7 +231,7 @@ def run_ours(args):
     total_steps = args.warmup + args.steps
     e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 5))
     e2e_warm = 0 if args.no_e2e else 2
-    headroom = total_steps + e2e_steps + e2e_warm + 8
+    headroom = total_steps + e2e_steps + e2e_warm + 24
 
     be = CudaCompute(layers, hq_l, hkv_l, d, n_slots=seqs, max_context=ctx + headroom, chunk_cap=1,
                      kv_dtype=KvDtype.F16, device=local_rank)
@@ -288,30 +289,81 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    for w in range(args.warmup):
-        device_step(w, position)
-        position += 1
-    barrier()
-
-    be.profile_enable(args.steps * layers * 2 + 8)
-    launches0 = be.stats()["kernel_launches"]
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
-    ctx_first = position
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record(stream)
-    for s in range(args.steps):
-        device_step(args.warmup + s, position)
+    prof_steps = 0
+    if args.no_graph:
+        # Direct launches: one C-ABI call per layer per step, positions passed from the host.
+        for w in range(args.warmup):
+            device_step(w, position)
+            position += 1
+        barrier()
+        be.profile_enable(args.steps * layers * 2 + 8)
+        launches0 = be.stats()["kernel_launches"]
+        if sampler:
+            sampler.start()
+        ctx_first = position
+        barrier()
+        ev0.record(stream)
+        for s in range(args.steps):
+            device_step(args.warmup + s, position)
+            position += 1
+        ev1.record(stream)
+        barrier()
+        elapsed_ms = ev0.elapsed_time(ev1)
+        clocks = sampler.stop() if sampler else None
+        prof = be.profile_read()
+        be.profile_enable(0)
+        prof_steps = args.steps
+        launches = be.stats()["kernel_launches"] - launches0
+    else:
+        # One decode step (every layer: fused append + attention [+ all-gather], then the position advance) is
+        # captured once per input-pool entry as a CUDA graph over device-side positions, and replayed.
+        device_step(0, position)  # also brings NCCL up before any capture
         position += 1
-    ev1.record(stream)
-    barrier()
-    elapsed_ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if sampler else None
-    prof = be.profile_read()
-    be.profile_enable(0)
-    launches = be.stats()["kernel_launches"] - launches0
+        barrier()
+        replays = args.warmup + args.steps
+        be.resident_begin(slots, replays)
+        graphs = []
+        for i in range(pool):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for layer in range(layers):
+                    be.resident_layer(layer, q_in[i, layer].data_ptr(), k_in[i, layer].data_ptr(),
+                                      v_in[i, layer].data_ptr(), out[layer].data_ptr())
+                    if world > 1:
+                        dist.all_gather_into_tensor(gathered[layer], out[layer])
+                be.resident_advance()
+            graphs.append(g)
+        torch.cuda.set_stream(stream)
+        for w in range(args.warmup):
+            graphs[w % pool].replay()
+        barrier()
+        if sampler:
+            sampler.start()
+        ctx_first = position + args.warmup
+        barrier()
+        ev0.record(stream)
+        for s in range(args.steps):
+            graphs[(args.warmup + s) % pool].replay()
+        ev1.record(stream)
+        barrier()
+        elapsed_ms = ev0.elapsed_time(ev1)
+        clocks = sampler.stop() if sampler else None
+        be.resident_end(replays)
+        position += replays
+        launches = args.steps * (layers + 1)  # per rank: one fused kernel per layer plus the position advance
+        del graphs
+        # The same steps once more as direct launches with a CUDA-event pair around every kernel: the decode
+        # kernel's own duration for the roofline (identical kernel; events cannot bracket nodes of a replayed graph).
+        prof_steps = min(args.steps, 8)
+        be.profile_enable(prof_steps * layers * 2 + 8)
+        for s in range(prof_steps):
+            device_step(s, position)
+            position += 1
+        prof = be.profile_read()
+        be.profile_enable(0)
+        barrier()
     splits = be.stats()["last_splits"]
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
@@ -337,6 +389,7 @@ def run_ours(args):
                 "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
                 "kernel": "decode_f16_kernel<128,3>", "bytes_per_launch": bytes_launch_rank,
                 "avg_launch_ms": attn_ms, "launches_timed": prof["attention_launches"],
+                "timed_as": "event pair around every launch" + ("" if args.no_graph else ", direct-launch pass after the graph replays"),
                 "append_avg_launch_ms": prof["append_ms"] / max(prof["append_launches"], 1),
                 "kv_splits": splits,
                 "whole_step_kv_gbs": bytes_step_total / (ms_per_step * 1e-3) / 1e9}
@@ -389,6 +442,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "f32 math over an f16 KV cache", "data": "synthetic",
             "config": {"workload": args.workload, "layers": layers, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
                        "sequences": seqs, "context": ctx_first, "kv_dtype": "f16",
+                       "launch": "direct" if args.no_graph else "cuda graph per step over device-side positions",
                        "parallelism": f"kv-head shards x{world}" + (", NCCL all-gather per layer" if world > 1 else ""),
                        "l2": "inputs larger than L2: every layer streams its own KV, "
                              f"{bytes_launch_rank / 2**20:.0f} MiB per launch"},

@@ -161,6 +161,22 @@ int itk_attention_batch_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, 
                                const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
                                const float* d_v, float* d_out);
 
+/* A decode loop whose launches depend on no host-side position, so that one step can be recorded once (a
+ * CUDA graph) and replayed - the counterpart of the reference session's "one command buffer per forward"
+ * (crates/wgpu-compute/src/session.rs:3230-3233).  The listed slots must sit at one position on every layer,
+ * with an f16 cache and head_dim 64 or 128.
+ *   itk_resident_begin    reserves `max_steps` decode steps for the slots and writes their positions to the device
+ *   itk_resident_layer    one layer of the current step for all listed slots: stores the new K/V row and attends
+ *                         (device f32 q/out [n_seqs][q_heads*D], k/v [n_seqs][kv_heads*D]); only queues work
+ *   itk_resident_advance  queues the kernel that moves every listed slot to the next position (end of a step)
+ *   itk_resident_end      tells the backend how many steps actually ran, and leaves the mode
+ * Between begin and end no other call may touch the listed slots. */
+int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, uint64_t max_steps);
+int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
+                       float* d_out);
+int itk_resident_advance(itk_backend* b);
+int itk_resident_end(itk_backend* b, uint64_t steps_done);
+
 /* gqa_attention alone (crates/attention/src/attention.rs:104-215) over what a
  * slot already holds: `rows` queries at query_positions[], host buffers.
  * Refuses ITK_ERR_NO_VISIBLE_KEYS when a query sees nothing. */

@@ -87,6 +87,10 @@ SIGNATURES = {
     "itk_attention": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _sz, _u64, _vp]),
     "itk_attention_batch": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_attention_batch_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
+    "itk_resident_begin": (C.c_int, [_vp, _u32, _u32p, _u64]),
+    "itk_resident_layer": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
+    "itk_resident_advance": (C.c_int, [_vp]),
+    "itk_resident_end": (C.c_int, [_vp, _u64]),
     "itk_gqa_attention": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _u32, _u64p, _vp]),
     "itk_append": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _u64]),
     "itk_append_rows": (C.c_int, [_vp, _u32, _u32, _vp, _vp, _u32, _u64]),

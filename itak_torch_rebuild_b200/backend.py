@@ -207,6 +207,24 @@ class CudaCompute:
         self._check(fn(self._h, layer, n, slots_c, positions_c, rows, C.c_void_p(q_ptr), C.c_void_p(k_ptr),
                        C.c_void_p(v_ptr), C.c_void_p(out_ptr)))
 
+    # -- replayable decode loop ------------------------------------------------------------------
+    def resident_begin(self, slots: Sequence[int], max_steps: int):
+        """Reserve ``max_steps`` decode steps for ``slots`` and move their positions to device memory; the step's
+        launches (``resident_layer`` per layer, then ``resident_advance``) can then be captured once and replayed."""
+        n = len(slots)
+        sl = (C.c_uint32 * n)(*slots)
+        self._check(self._lib.itk_resident_begin(self._h, n, sl, max_steps))
+
+    def resident_layer(self, layer: int, q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int):
+        self._check(self._lib.itk_resident_layer(self._h, layer, C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(v_ptr),
+                                                 C.c_void_p(out_ptr)))
+
+    def resident_advance(self):
+        self._check(self._lib.itk_resident_advance(self._h))
+
+    def resident_end(self, steps_done: int):
+        self._check(self._lib.itk_resident_end(self._h, steps_done))
+
     def gqa_attention(self, layer: int, q, query_positions: Sequence[int], slot: int = 0) -> np.ndarray:
         """``gqa_attention`` over what the slot already holds; one query row per listed position."""
         q = _host_f32(q).reshape(-1)

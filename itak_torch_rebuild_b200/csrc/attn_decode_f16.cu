@@ -56,6 +56,22 @@ struct TileCursor {
     uint32_t slot;
 };
 
+// The i-th sequence of the launch, from the parameters or from device-resident state.
+__device__ __forceinline__ SeqDesc seq_of(const AttnLaunch& p, uint32_t i) {
+    if (p.seq_dev == nullptr) return p.seq[i];
+    const SeqState st = p.seq_dev[i];
+    SeqDesc d;
+    d.slot = st.slot;
+    d.q_pos0 = st.pos;
+    d.kv_hi = st.pos + 1;
+    d.kv_lo = (p.layer.window != 0 && st.pos + 1 > p.layer.window) ? st.pos + 1 - p.layer.window : 0u;
+    return d;
+}
+
+__global__ void advance_states_kernel(SeqState* states, uint32_t n) {
+    if (threadIdx.x < n) states[threadIdx.x].pos += 1;
+}
+
 template <int D, int STAGES>
 __host__ __device__ constexpr size_t decode_pipe_bytes() {
     return static_cast<size_t>(STAGES) * kDecodeWarps * 2 * 16 * D * 2;
@@ -99,19 +115,20 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         uint32_t c = 0;
         for (uint32_t s = 0; s < p.n_seqs; ++s) {
             cum[s] = c;
-            c += (p.seq[s].kv_hi - p.seq[s].kv_lo + kTileKeys - 1) / kTileKeys * HY;
+            const SeqDesc sd = seq_of(p, s);
+            c += (sd.kv_hi - sd.kv_lo + kTileKeys - 1) / kTileKeys * HY;
         }
         cum[p.n_seqs] = c;
     }
     __syncthreads();
     const uint32_t total = cum[p.n_seqs];
-    const uint32_t per = p.tiles_per_cta;
+    const uint32_t per = p.seq_dev ? (total + gridDim.x - 1) / gridDim.x : p.tiles_per_cta;
     const uint32_t g0 = blockIdx.x * per;
     if (g0 >= total) return;
     const uint32_t ntiles = min(total, g0 + per) - g0;
 
     auto enter_seq = [&](TileCursor& c) {
-        const SeqDesc sd = p.seq[c.seq];
+        const SeqDesc sd = seq_of(p, c.seq);
         c.n = sd.kv_hi - sd.kv_lo;
         c.T = (c.n + kTileKeys - 1) / kTileKeys;
         c.s0 = sd.kv_lo % ring;
@@ -391,9 +408,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
 constexpr int kStages128 = 3;  // 96 KiB of pipeline per CTA at D = 128, two CTAs per SM
 constexpr int kStages64 = 4;   // 64 KiB at D = 64
 
-// Most CTAs that can share a cell of T tiles when every CTA walks `per` tiles.
-uint32_t parts_for(uint32_t T, uint32_t per) { return (T + per - 2) / per + 1; }
-
 }  // namespace
 
 bool decode_f16_supported(uint32_t head_dim, uint32_t rows) {
@@ -428,10 +442,10 @@ cudaError_t launch_decode_f16(AttnLaunch p, uint32_t cta_slots, uint32_t max_par
     if (cta_slots == 0) cta_slots = 1;
     uint64_t ctas = total < cta_slots ? total : cta_slots;
     uint32_t per = static_cast<uint32_t>((total + ctas - 1) / ctas);
-    while (parts_for(tmax, per) > max_parts) ++per;  // fewer, longer runs when the scratch bounds the sharing
+    while (decode_parts_for(tmax, per) > max_parts) ++per;  // fewer, longer runs when the scratch bounds the sharing
     ctas = (total + per - 1) / per;
     p.tiles_per_cta = per;
-    p.splits = parts_for(tmax, per);
+    p.splits = decode_parts_for(tmax, per);
     if (parts_used) *parts_used = p.splits;
     const dim3 grid(static_cast<unsigned int>(ctas));
     if (p.layer.head_dim == 128) {
@@ -441,6 +455,32 @@ cudaError_t launch_decode_f16(AttnLaunch p, uint32_t cta_slots, uint32_t max_par
     } else {
         return cudaErrorInvalidValue;
     }
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t parts_stride, cudaStream_t s,
+                                       uint64_t* launches) {
+    if (!p.seq_dev || p.n_seqs == 0 || p.n_seqs > static_cast<uint32_t>(kMaxSeqsPerLaunch) || p.rows != 1 || ctas == 0 ||
+        parts_stride < 2 || parts_stride > kDecodeMaxParts)
+        return cudaErrorInvalidValue;
+    p.tiles_per_cta = 0;
+    p.splits = parts_stride;
+    const dim3 grid(ctas);
+    if (p.layer.head_dim == 128) {
+        decode_f16_kernel<128, kStages128><<<grid, kDecodeThreads, decode_smem_bytes<128, kStages128>(), s>>>(p);
+    } else if (p.layer.head_dim == 64) {
+        decode_f16_kernel<64, kStages64><<<grid, kDecodeThreads, decode_smem_bytes<64, kStages64>(), s>>>(p);
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, uint64_t* launches) {
+    if (!states || n == 0 || n > static_cast<uint32_t>(kMaxSeqsPerLaunch)) return cudaErrorInvalidValue;
+    advance_states_kernel<<<1, kMaxSeqsPerLaunch, 0, s>>>(states, n);
     if (launches) *launches += 1;
     return cudaGetLastError();
 }

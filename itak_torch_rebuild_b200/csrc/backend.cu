@@ -92,6 +92,12 @@ struct itk_backend {
     int forced_ctas = 0;         // ITK_DECODE_CTAS: persistent CTAs of the decode kernel (default 2 per SM)
     bool separate_append = false;  // ITK_SEPARATE_APPEND=1: decode steps launch the append kernel separately
     bool force_general = false;  // ITK_FORCE_GENERAL=1: multi-row launches take the CUDA-core kernel (A/B checks)
+    // resident decode loop (device-side sequence states, replayable)
+    itk::SeqState* d_states = nullptr;
+    bool res_active = false;
+    std::vector<uint32_t> res_slots;
+    uint64_t res_max_steps = 0;
+    uint32_t res_ctas = 0, res_parts = 0;
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
@@ -527,6 +533,8 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (e == cudaSuccess) e = cudaMalloc(&b->d_k, b->stage_rows * b->row_len() * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&b->d_v, b->stage_rows * b->row_len() * sizeof(float));
     if (e != cudaSuccess) return cuda_refuse(e, "staging allocation");
+    e = cudaMalloc(&b->d_states, itk::kMaxSeqsPerLaunch * sizeof(itk::SeqState));
+    if (e != cudaSuccess) return cuda_refuse(e, "sequence-state allocation");
     e = cudaStreamSynchronize(b->stream);
     if (e != cudaSuccess) return cuda_refuse(e, "initialisation");
     b->slots.resize(cfg->n_slots);
@@ -553,6 +561,7 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->d_v);
     cudaFree(b->d_out);
     cudaFree(b->gather_buf);
+    cudaFree(b->d_states);
     for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
     if (b->own_stream) cudaStreamDestroy(b->own_stream);
     delete b;
@@ -575,6 +584,135 @@ int itk_synchronize(itk_backend* b) {
 int itk_get_stats(const itk_backend* b, itk_stats* out) {
     if (!b || !out) return ITK_ERR_INVALID_ARGUMENT;
     *out = b->stats;
+    return ITK_OK;
+}
+
+int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, uint64_t max_steps) {
+    if (!b || !slots) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: already active; end it first");
+    if (!(b->f16 && itk::decode_f16_supported(b->cfg.head_dim, 1)))
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: needs an f16 cache with head_dim 64 or 128");
+    if (n_seqs == 0 || n_seqs > static_cast<uint32_t>(itk::kMaxSeqsPerLaunch) || max_steps == 0)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: 1..64 sequences and at least one step");
+    std::vector<itk::SeqState> states(n_seqs);
+    const uint32_t HY = b->cfg.kv_heads * b->gchunks;
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        if (int rc = check_slot(b, slots[i])) return rc;
+        for (uint32_t j = 0; j < i; ++j)
+            if (slots[j] == slots[i])
+                return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: slot " + zu(slots[i]) + " listed twice");
+        const SlotState& st = b->slots[slots[i]];
+        const uint64_t pos = st.appended[0];
+        for (uint32_t l = 0; l < b->cfg.n_layers; ++l) {
+            if (st.appended[l] != pos)
+                return b->fail(ITK_ERR_INCOHERENT_CACHE, "resident loop: layer 0 has appended " + zu(pos) +
+                                                             " positions but layer " + zu(l) + " has appended " +
+                                                             zu(st.appended[l]));
+            if (b->window[l] == 0 && pos + max_steps > b->ring[l])
+                return b->fail(ITK_ERR_CAPACITY, "resident loop: position " + zu(pos + max_steps) +
+                                                     " is past the slot's context capacity of " + zu(b->ring[l]));
+            if (st.live && pos + max_steps > st.bases[l] + st.max_round)
+                return b->fail(ITK_ERR_CHECKPOINT_RANGE_EXCEEDED,
+                               "resident loop: layer " + zu(l) + " append at position " + zu(st.bases[l] + st.max_round) +
+                                   " is outside the live checkpoint's saved range");
+        }
+        if (pos + max_steps > 0xfffffff0ull) return b->fail(ITK_ERR_CAPACITY, "resident loop: position exceeds 32 bits");
+        states[i].slot = slots[i];
+        states[i].pos = static_cast<uint32_t>(pos);
+    }
+    // One grid for every layer and every step of the loop: the largest one (at most two CTAs per SM) that keeps
+    // each cell within the scratch's partial slots on every layer, at the first and at the last step.
+    const uint64_t cells = static_cast<uint64_t>(n_seqs) * HY;
+    uint64_t cap = kPartCellSplits / cells;
+    if (cap > itk::kDecodeMaxParts) cap = itk::kDecodeMaxParts;
+    if (cap < 2 || cells > b->ticket_cells) return b->fail(ITK_ERR_CAPACITY, "resident loop: too many (sequence, head) cells");
+    // per layer: (largest cell, all cells) in tiles at the first and last step
+    auto tiles_at = [&](uint32_t l, uint64_t extra, uint64_t* tmax, uint64_t* total) {
+        *tmax = 0;
+        *total = 0;
+        for (uint32_t i = 0; i < n_seqs; ++i) {
+            uint64_t n = static_cast<uint64_t>(states[i].pos) + 1 + extra;
+            if (b->window[l] && n > b->window[l]) n = b->window[l];
+            const uint64_t t = (n + 63) / 64;
+            if (t > *tmax) *tmax = t;
+            *total += t * HY;
+        }
+    };
+    uint64_t ctas = b->forced_ctas > 0 ? static_cast<uint64_t>(b->forced_ctas) : 2ull * b->sm_count;
+    auto fits = [&](uint64_t g) {
+        for (uint32_t l = 0; l < b->cfg.n_layers; ++l) {
+            uint64_t ts, tots, te, tote;
+            tiles_at(l, 0, &ts, &tots);
+            tiles_at(l, max_steps - 1, &te, &tote);
+            const uint32_t ps = static_cast<uint32_t>((tots + g - 1) / g), pe = static_cast<uint32_t>((tote + g - 1) / g);
+            if (itk::decode_parts_for(static_cast<uint32_t>(ts), ps) > cap ||
+                itk::decode_parts_for(static_cast<uint32_t>(te), pe) > cap ||
+                itk::decode_parts_for(static_cast<uint32_t>(te), ps) > cap)
+                return false;
+        }
+        return true;
+    };
+    while (ctas > 1 && !fits(ctas)) --ctas;
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_states, states.data(), n_seqs * sizeof(itk::SeqState), cudaMemcpyHostToDevice,
+                                b->stream), "sequence-state upload");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
+    b->res_active = true;
+    b->res_slots.assign(slots, slots + n_seqs);
+    b->res_max_steps = max_steps;
+    b->res_ctas = static_cast<uint32_t>(ctas);
+    b->res_parts = static_cast<uint32_t>(cap);
+    return ITK_OK;
+}
+
+int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
+                       float* d_out) {
+    if (!b || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+    if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
+    if (int rc = check_layer(b, layer)) return rc;
+    AttnLaunch p{};
+    fill_layer_view(b, layer, &p.layer);
+    p.q = d_q;
+    p.out = d_out;
+    p.part_o = b->part_o;
+    p.part_ml = b->part_ml;
+    p.tickets = b->tickets;
+    p.q_heads = b->cfg.q_heads;
+    p.group = b->group;
+    p.gchunks = b->gchunks;
+    p.rows = 1;
+    p.n_seqs = static_cast<uint32_t>(b->res_slots.size());
+    p.scale = 1.0f / sqrtf(static_cast<float>(b->cfg.head_dim));
+    p.k_new = d_k;
+    p.v_new = d_v;
+    p.seq_dev = b->d_states;
+    ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
+             "resident decode launch");
+    return ITK_OK;
+}
+
+int itk_resident_advance(itk_backend* b) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
+    ITK_CUDA(b, itk::launch_advance_states(b->d_states, static_cast<uint32_t>(b->res_slots.size()), b->stream,
+                                           &b->stats.kernel_launches), "state advance launch");
+    return ITK_OK;
+}
+
+int itk_resident_end(itk_backend* b, uint64_t steps_done) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
+    if (steps_done > b->res_max_steps)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: " + zu(steps_done) + " steps reported, " +
+                                                     zu(b->res_max_steps) + " were reserved");
+    for (uint32_t slot : b->res_slots) {
+        SlotState& st = b->slots[slot];
+        for (uint32_t l = 0; l < b->cfg.n_layers; ++l) st.appended[l] += steps_done;
+        if (steps_done) st.built = true;
+    }
+    b->stats.rows_appended += steps_done * b->res_slots.size() * b->cfg.n_layers;
+    b->stats.attention_calls += steps_done * b->cfg.n_layers;
+    b->res_active = false;
     return ITK_OK;
 }
 

@@ -34,6 +34,13 @@ struct SeqDesc {
     uint32_t kv_hi;   // one past the last position (q_pos0 + rows)
 };
 
+// Device-resident form of a decode step's sequence list: the kernels derive kv_lo / kv_hi from the position,
+// and a one-block kernel advances the positions, so a captured step can be replayed without host updates.
+struct SeqState {
+    uint32_t slot;
+    uint32_t pos;  // position of the step's query = position its new row is stored at
+};
+
 struct LayerView {
     const void* k;      // layer base of the K slab (element type by dtype)
     const void* v;      // layer base of the V slab
@@ -60,6 +67,8 @@ struct AttnLaunch {
     uint32_t tiles_per_cta;  // decode kernel: 64-key tiles each persistent CTA walks
     const float* k_new;      // decode kernel: when set, the step's new K rows [n_seqs][kv_heads][D] (f32); the
     const float* v_new;      // kernel stores them at position kv_hi - 1 itself instead of a separate append
+    const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
+                             // tiles_per_cta is derived in the kernel from the grid size
     float scale;             // score scale, 1/sqrt(D) by default
     SeqDesc seq[kMaxSeqsPerLaunch];
 };
@@ -110,6 +119,14 @@ cudaError_t launch_convert(const float* src, void* dst, size_t n, bool f16, cuda
 cudaError_t launch_decode_f16(AttnLaunch p, uint32_t cta_slots, uint32_t max_parts, cudaStream_t s,
                               uint64_t* launches, uint32_t* parts_used);
 constexpr uint32_t kDecodeMaxParts = 64;
+// The same kernel over device-resident sequence states (p.seq_dev, p.n_seqs set by the caller): `ctas` CTAs,
+// `parts_stride` partial slots per cell.  Nothing in the launch depends on host-side positions.
+cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t parts_stride, cudaStream_t s,
+                                       uint64_t* launches);
+// pos += 1 for the first n states.
+cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, uint64_t* launches);
+// Most CTAs that can share a cell of T tiles when every CTA walks `per` tiles.
+inline uint32_t decode_parts_for(uint32_t T, uint32_t per) { return (T + per - 2) / per + 1; }
 bool decode_f16_supported(uint32_t head_dim, uint32_t rows);
 // Multi-row causal attention over an f16 cache (chunked prefill / speculative verify).
 cudaError_t launch_verify_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);

@@ -1,0 +1,122 @@
+"""The replayable decode loop (device-side positions): its steps equal the ordinary per-layer step calls, both
+when launched directly and when one step is captured in a CUDA graph and replayed."""
+import numpy as np
+import pytest
+
+from itak_torch_rebuild_b200 import CudaCompute, CudaComputeError, KvDtype, _lib
+
+from kvparity import assert_view_equal, attention_error, make_pair, stored
+
+pytestmark = pytest.mark.gpu
+
+
+def build(layer_window, hq, hkv, d, lens, cap, seed):
+    gpu, refs = make_pair(layer_window, hq, hkv, d, dtype=KvDtype.F16, n_slots=len(lens), max_context=cap, chunk_cap=1)
+    rng = np.random.default_rng(seed)
+    for slot, n in enumerate(lens):
+        for layer in range(len(layer_window)):
+            k = rng.standard_normal((n, hkv * d)).astype(np.float32)
+            v = rng.standard_normal((n, hkv * d)).astype(np.float32)
+            at = 0
+            while at < n:  # one row at a time on ring layers (chunk cap 1), bulk on global ones
+                m = n - at if layer_window[layer] == 0 else 1
+                gpu.append_rows(layer, k[at:at + m], v[at:at + m], at, slot=slot)
+                at += m
+            refs[slot].append_rows(layer, stored(k, KvDtype.F16), stored(v, KvDtype.F16), 0)
+    return gpu, refs
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_resident_steps_equal_ordinary_steps(use_graph):
+    import torch
+
+    layer_window, hq, hkv, d = [0, 48], 32, 8, 128
+    lens, steps = [300, 70, 515], 5
+    layers, n = len(layer_window), len(lens)
+    a, refs = build(layer_window, hq, hkv, d, lens, 600, seed=3)   # resident loop
+    b, _ = build(layer_window, hq, hkv, d, lens, 600, seed=3)      # ordinary calls
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev)
+    a.set_stream(stream.cuda_stream)
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((steps, layers, n, hq * d)).astype(np.float32)
+    k = rng.standard_normal((steps, layers, n, hkv * d)).astype(np.float32)
+    v = rng.standard_normal((steps, layers, n, hkv * d)).astype(np.float32)
+    # the step's inputs live in fixed device buffers (a captured step reads the same addresses every replay)
+    q_d = torch.empty((layers, n, hq * d), device=dev)
+    k_d = torch.empty((layers, n, hkv * d), device=dev)
+    v_d = torch.empty((layers, n, hkv * d), device=dev)
+    out_d = torch.empty((layers, n, hq * d), device=dev)
+
+    def step_launches():
+        for layer in range(layers):
+            a.resident_layer(layer, q_d[layer].data_ptr(), k_d[layer].data_ptr(), v_d[layer].data_ptr(),
+                             out_d[layer].data_ptr())
+        a.resident_advance()
+
+    slots = list(range(n))
+    a.resident_begin(slots, steps)
+    with pytest.raises(CudaComputeError) as e:
+        a.resident_begin(slots, steps)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT
+    graph = None
+    with torch.cuda.stream(stream):
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step_launches()
+        for s in range(steps):
+            q_d.copy_(torch.from_numpy(q[s]))
+            k_d.copy_(torch.from_numpy(k[s]))
+            v_d.copy_(torch.from_numpy(v[s]))
+            if graph is not None:
+                graph.replay()
+            else:
+                step_launches()
+            stream.synchronize()
+            got = out_d.cpu().numpy()
+            for layer in range(layers):
+                want = b.attention_batch(layer, slots, [lens[i] + s for i in range(n)], 1, q[s, layer], k[s, layer],
+                                         v[s, layer]).reshape(n, -1)
+                # the two routes may cut the key ranges differently (different f32 summation order)
+                assert attention_error(got[layer], want, hq, d) <= 1e-5, f"step {s} layer {layer}"
+    a.resident_end(steps)
+    for slot in range(n):
+        for layer in range(layers):
+            assert a.next_position(layer, slot=slot) == lens[slot] + steps
+            fa, ka, va = a.view(layer, slot=slot)
+            fb, kb, vb = b.view(layer, slot=slot)
+            assert fa == fb and ka.tobytes() == kb.tobytes() and va.tobytes() == vb.tobytes()
+    # and the loop's cache equals the oracle fed the same rows
+    for slot in range(n):
+        for s in range(steps):
+            for layer in range(layers):
+                refs[slot].append(layer, stored(k[s, layer, slot], KvDtype.F16), stored(v[s, layer, slot], KvDtype.F16),
+                                  lens[slot] + s)
+        for layer in range(layers):
+            assert_view_equal(a, refs[slot], layer, KvDtype.F16, slot=slot)
+
+
+def test_resident_loop_refusals():
+    gpu = CudaCompute(2, 8, 2, 64, n_slots=2, max_context=16, chunk_cap=1, kv_dtype=KvDtype.F16)
+    gpu.append(0, np.zeros(128), np.zeros(128), 0)
+    with pytest.raises(CudaComputeError) as e:  # layers at different positions
+        gpu.resident_begin([0], 2)
+    assert e.value.code == _lib.ERR_INCOHERENT_CACHE
+    gpu.append(1, np.zeros(128), np.zeros(128), 0)
+    with pytest.raises(CudaComputeError) as e:  # past the context capacity
+        gpu.resident_begin([0], 16)
+    assert e.value.code == _lib.ERR_CAPACITY
+    with pytest.raises(CudaComputeError) as e:
+        gpu.resident_layer(0, 1, 1, 1, 1)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT and "not active" in e.value.msg
+    gpu.resident_begin([0], 4)
+    with pytest.raises(CudaComputeError) as e:
+        gpu.resident_end(5)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT
+    gpu.resident_end(0)
+    assert gpu.next_position(0) == 1
+    f32 = CudaCompute(1, 8, 2, 64, n_slots=1, max_context=16, chunk_cap=1, kv_dtype=KvDtype.F32)
+    with pytest.raises(CudaComputeError) as e:
+        f32.resident_begin([0], 1)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT
