@@ -353,7 +353,7 @@ def run_ours(args):
         be.resident_end(replays)
         position += replays
         launches = args.steps * (layers + 1)  # per rank: one fused kernel per layer plus the position advance
-        del graphs
+        del graphs, g
         # The same steps once more as direct launches with a CUDA-event pair around every kernel: the decode
         # kernel's own duration for the roofline (identical kernel; events cannot bracket nodes of a replayed graph).
         prof_steps = min(args.steps, 8)
@@ -451,9 +451,14 @@ def run_ours(args):
             "roofline": roofline, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks, "gpu_launches": launches,
         }
         print(json.dumps(line), flush=True)
-    be.close()
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the communicator down: NCCL teardown after graph capture has been seen to wait
+        # forever, and there is nothing left to release that process exit does not release.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+    be.close()
 
 
 def main():
