@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--workload", default="c5_long_context_decode", choices=sorted(WORKLOADS))
     ap.add_argument("--context", type=int, default=None, help="override the context length (smoke runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (smoke runs)")
+    ap.add_argument("--q-heads", type=int, default=None, help="override the query head count (shard studies)")
+    ap.add_argument("--kv-heads", type=int, default=None, help="override the KV head count (shard studies)")
+    ap.add_argument("--sequences", type=int, default=None, help="override the number of resident sequences")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer directly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -61,6 +64,12 @@ def geometry(args):
         ctx = args.context
     if args.layers:
         layers = args.layers
+    if args.q_heads:
+        hq = args.q_heads
+    if args.kv_heads:
+        hkv = args.kv_heads
+    if args.sequences:
+        seqs = args.sequences
     return layers, hq, hkv, d, seqs, ctx
 
 

@@ -142,24 +142,48 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
         inv_l[tid] = 1.f / L;
     }
     __syncthreads();
-    for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
-        const uint32_t h = idx / D;
-        const float* src = all_o + idx;
-        float acc = 0.f;
-        uint32_t s = 0;
-        for (; s + 4 <= n_parts; s += 4) {
-            const float o0 = __ldcg(src + static_cast<size_t>(s) * (kHeadsPerCta * D));
-            const float o1 = __ldcg(src + static_cast<size_t>(s + 1) * (kHeadsPerCta * D));
-            const float o2 = __ldcg(src + static_cast<size_t>(s + 2) * (kHeadsPerCta * D));
-            const float o3 = __ldcg(src + static_cast<size_t>(s + 3) * (kHeadsPerCta * D));
-            acc += w_m[s * kHeadsPerCta + h] * o0;
-            acc += w_m[(s + 1) * kHeadsPerCta + h] * o1;
-            acc += w_m[(s + 2) * kHeadsPerCta + h] * o2;
-            acc += w_m[(s + 3) * kHeadsPerCta + h] * o3;
+    if ((D & 3u) == 0) {
+        // Vector path: a thread owns up to two float4 columns and keeps 8 parts x 2 columns of loads in flight,
+        // so merging a cell that dozens of CTAs shared costs a few memory round trips, not dozens.
+        const uint32_t cols = nh * D / 4;
+        const size_t pstride = kHeadsPerCta * D / 4;  // float4s per part
+        const float4* src4 = reinterpret_cast<const float4*>(all_o);
+        float4* out4 = reinterpret_cast<float4*>(out);
+        for (uint32_t c0 = tid; c0 < cols; c0 += 2 * THREADS) {
+            const uint32_t c1 = c0 + THREADS;
+            const bool two = c1 < cols;
+            const uint32_t h0 = (c0 * 4) / D, h1 = two ? (c1 * 4) / D : h0;
+            float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+            for (uint32_t s = 0; s < n_parts; s += 8) {
+                float4 v0[8], v1[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t si = s + i < n_parts ? s + i : s;  // clamped; its weight is zeroed below
+                    v0[i] = __ldcg(src4 + si * pstride + c0);
+                    v1[i] = two ? __ldcg(src4 + si * pstride + c1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const bool ok = s + i < n_parts;
+                    const float w0 = ok ? w_m[(s + i) * kHeadsPerCta + h0] : 0.f;
+                    const float w1 = ok ? w_m[(s + i) * kHeadsPerCta + h1] : 0.f;
+                    a0.x += w0 * v0[i].x; a0.y += w0 * v0[i].y; a0.z += w0 * v0[i].z; a0.w += w0 * v0[i].w;
+                    a1.x += w1 * v1[i].x; a1.y += w1 * v1[i].y; a1.z += w1 * v1[i].z; a1.w += w1 * v1[i].w;
+                }
+            }
+            const float i0 = inv_l[h0], i1 = inv_l[h1];
+            out4[c0] = make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0);
+            if (two) out4[c1] = make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1);
         }
-        for (; s < n_parts; ++s)
-            acc += w_m[s * kHeadsPerCta + h] * __ldcg(src + static_cast<size_t>(s) * (kHeadsPerCta * D));
-        out[idx] = acc * inv_l[h];
+    } else {
+        for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
+            const uint32_t h = idx / D;
+            const float* src = all_o + idx;
+            float acc = 0.f;
+            for (uint32_t s = 0; s < n_parts; ++s)
+                acc += w_m[s * kHeadsPerCta + h] * __ldcg(src + static_cast<size_t>(s) * (kHeadsPerCta * D));
+            out[idx] = acc * inv_l[h];
+        }
     }
     if (tid == 0) p.tickets[cell] = 0u;
 }
