@@ -68,6 +68,11 @@ __device__ __forceinline__ SeqDesc seq_of(const AttnLaunch& p, uint32_t i) {
     return d;
 }
 
+// Programmatic dependent launch: let the next kernel in the stream be scheduled early / wait until the
+// previous one has completed and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
 __global__ void advance_states_kernel(SeqState* states, uint32_t n) {
     if (threadIdx.x < n) states[threadIdx.x].pos += 1;
 }
@@ -110,6 +115,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
     const bool fused = p.k_new != nullptr;
 
+    if (p.pdl != 0) pdl_launch_dependents();
+    if (p.pdl == 1) pdl_wait();
     // cum[s] = tiles of all cells before sequence s
     if (tid == 0) {
         uint32_t c = 0;
@@ -124,7 +131,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     const uint32_t total = cum[p.n_seqs];
     const uint32_t per = p.seq_dev ? (total + gridDim.x - 1) / gridDim.x : p.tiles_per_cta;
     const uint32_t g0 = blockIdx.x * per;
-    if (g0 >= total) return;
+    if (g0 >= total) {
+        if (p.pdl == 2) pdl_wait();
+        return;
+    }
     const uint32_t ntiles = min(total, g0 + per) - g0;
 
     auto enter_seq = [&](TileCursor& c) {
@@ -193,6 +203,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         }
         cp_async_commit();
     }
+
+    // The cache rows streamed above do not depend on the previous kernel; the queries, the step's new row
+    // and the merge scratch do.
+    if (p.pdl == 2) pdl_wait();
 
     uint32_t qa[KS][4];
     float o[NT][4];
@@ -466,14 +480,26 @@ cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t par
         return cudaErrorInvalidValue;
     p.tiles_per_cta = 0;
     p.splits = parts_stride;
-    const dim3 grid(ctas);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kDecodeThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl != 0 ? 1 : 0;
+    cudaError_t e;
     if (p.layer.head_dim == 128) {
-        decode_f16_kernel<128, kStages128><<<grid, kDecodeThreads, decode_smem_bytes<128, kStages128>(), s>>>(p);
+        cfg.dynamicSmemBytes = decode_smem_bytes<128, kStages128>();
+        e = cudaLaunchKernelEx(&cfg, decode_f16_kernel<128, kStages128>, p);
     } else if (p.layer.head_dim == 64) {
-        decode_f16_kernel<64, kStages64><<<grid, kDecodeThreads, decode_smem_bytes<64, kStages64>(), s>>>(p);
+        cfg.dynamicSmemBytes = decode_smem_bytes<64, kStages64>();
+        e = cudaLaunchKernelEx(&cfg, decode_f16_kernel<64, kStages64>, p);
     } else {
         return cudaErrorInvalidValue;
     }
+    if (e != cudaSuccess) return e;
     if (launches) *launches += 1;
     return cudaGetLastError();
 }

@@ -98,6 +98,8 @@ struct itk_backend {
     std::vector<uint32_t> res_slots;
     uint64_t res_max_steps = 0;
     uint32_t res_ctas = 0, res_parts = 0;
+    int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
+    bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
@@ -541,6 +543,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     for (uint32_t s = 0; s < cfg->n_slots; ++s) drop_slot(b, s);
     if (const char* env = std::getenv("ITK_DECODE_SPLITS")) b->forced_splits = std::atoi(env);
     if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
+    if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     *out = b;
@@ -662,6 +665,7 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
     b->res_max_steps = max_steps;
     b->res_ctas = static_cast<uint32_t>(ctas);
     b->res_parts = static_cast<uint32_t>(cap);
+    b->res_prev_layer = -1;
     return ITK_OK;
 }
 
@@ -686,8 +690,12 @@ int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const f
     p.k_new = d_k;
     p.v_new = d_v;
     p.seq_dev = b->d_states;
+    // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
+    // the same layer) the kernel waits first.
+    p.pdl = !b->use_pdl ? 0u : ((b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer) ? 2u : 1u);
     ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
              "resident decode launch");
+    b->res_prev_layer = static_cast<int>(layer);
     return ITK_OK;
 }
 
@@ -696,6 +704,7 @@ int itk_resident_advance(itk_backend* b) {
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
     ITK_CUDA(b, itk::launch_advance_states(b->d_states, static_cast<uint32_t>(b->res_slots.size()), b->stream,
                                            &b->stats.kernel_launches), "state advance launch");
+    b->res_prev_layer = -1;
     return ITK_OK;
 }
 

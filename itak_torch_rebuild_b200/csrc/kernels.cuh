@@ -67,6 +67,9 @@ struct AttnLaunch {
     uint32_t tiles_per_cta;  // decode kernel: 64-key tiles each persistent CTA walks
     const float* k_new;      // decode kernel: when set, the step's new K rows [n_seqs][kv_heads][D] (f32); the
     const float* v_new;      // kernel stores them at position kv_hi - 1 itself instead of a separate append
+    uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
+                             // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
+                             // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
     float scale;             // score scale, 1/sqrt(D) by default
@@ -123,6 +126,7 @@ constexpr uint32_t kDecodeMaxParts = 64;
 // `parts_stride` partial slots per cell.  Nothing in the launch depends on host-side positions.
 cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t parts_stride, cudaStream_t s,
                                        uint64_t* launches);
+// pdl != 0 launches with programmatic stream serialization (see AttnLaunch::pdl).
 // pos += 1 for the first n states.
 cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, uint64_t* launches);
 // Most CTAs that can share a cell of T tiles when every CTA walks `per` tiles.
