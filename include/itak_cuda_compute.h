@@ -55,7 +55,12 @@ typedef enum itk_status {
     ITK_ERR_REWIND_OUT_OF_RANGE = 14,
     ITK_ERR_INCOHERENT_CACHE = 32,
     ITK_ERR_INCONSISTENT_SNAPSHOT = 33,
+    ITK_ERR_BAD_MAGIC = 34,
+    ITK_ERR_UNSUPPORTED_VERSION = 35,
+    ITK_ERR_TRUNCATED = 36,
+    ITK_ERR_CHECKSUM_MISMATCH = 37,
     ITK_ERR_GEOMETRY_MISMATCH = 38,
+    ITK_ERR_FINGERPRINT_MISMATCH = 39,
     ITK_ERR_STEP_FAILED = 64,
     ITK_ERR_CUDA = 100,
     ITK_ERR_INVALID_ARGUMENT = 101,
@@ -257,6 +262,20 @@ int itk_snapshot_layer_to_host(itk_backend* b, const itk_snapshot* snap, uint32_
 int itk_snapshot_from_host_f32(itk_backend* b, uint64_t token_count, const uint64_t* first_position,
                                const uint64_t* rows, const float* const* keys, const float* const* values,
                                itk_snapshot** out);
+
+/* KvSnapshot::to_bytes (crates/itak-kv/src/snapshot.rs:13-29, 381-415): the versioned `ITKV` byte format -
+ * magic, version 1, model fingerprint, token count, KV heads, head dim, per-layer headers (kind, window, first
+ * position, row count), per-layer keys then values as little-endian f32, FNV-1a-64 checksum.  An f16 cache is
+ * written as the exact f32 values of its elements, so the bytes are an ordinary version-1 snapshot.  Two-call
+ * protocol: with out == NULL only *size is set. */
+int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* snap, const char* model_fingerprint, uint8_t* out,
+                         size_t capacity, size_t* size);
+/* KvSnapshot::from_bytes followed by restore_checked's trust checks (snapshot.rs:425-540, 345-371): strict
+ * decode (bad magic, unknown version, truncation, layer count beyond the buffer, overflowing products, trailing
+ * bytes, checksum, self-consistency - each a named refusal), then the backend's geometry and, when
+ * expected_fingerprint is not NULL, the model fingerprint.  Rows are cast to the cache's element type. */
+int itk_snapshot_from_itkv(itk_backend* b, const uint8_t* bytes, size_t n, const char* expected_fingerprint,
+                           itk_snapshot** out);
 
 /* ---- for callers that cannot allocate ------------------------------------------------ */
 

@@ -25,7 +25,12 @@ ERR_BULK_RESTORE_NOT_FRESH = 13
 ERR_REWIND_OUT_OF_RANGE = 14
 ERR_INCOHERENT_CACHE = 32
 ERR_INCONSISTENT_SNAPSHOT = 33
+ERR_BAD_MAGIC = 34
+ERR_UNSUPPORTED_VERSION = 35
+ERR_TRUNCATED = 36
+ERR_CHECKSUM_MISMATCH = 37
 ERR_GEOMETRY_MISMATCH = 38
+ERR_FINGERPRINT_MISMATCH = 39
 ERR_STEP_FAILED = 64
 ERR_CUDA = 100
 ERR_INVALID_ARGUMENT = 101
@@ -112,6 +117,8 @@ SIGNATURES = {
     "itk_snapshot_payload_bytes": (_u64, [_vp]),
     "itk_snapshot_layer_to_host": (C.c_int, [_vp, _vp, _u32, _vp, _vp, _u64p, _u64p]),
     "itk_snapshot_from_host_f32": (C.c_int, [_vp, _u64, _u64p, _u64p, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
+    "itk_snapshot_to_itkv": (C.c_int, [_vp, _vp, C.c_char_p, _vp, _sz, C.POINTER(_sz)]),
+    "itk_snapshot_from_itkv": (C.c_int, [_vp, C.c_char_p, _sz, C.c_char_p, C.POINTER(_vp)]),
     "itk_decode_attention_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _vp, _vp, _u32, _vp,
                                                C.c_char_p, _sz]),
 }

@@ -92,6 +92,15 @@ class DeviceSnapshot:
     def payload_bytes(self) -> int:
         return _lib.load().itk_snapshot_payload_bytes(self._h)
 
+    def to_itkv(self, model_fingerprint: str) -> bytes:
+        """The snapshot in the reference's versioned ``ITKV`` byte format (f32 rows, FNV-1a-64 checksum)."""
+        b = self._owner
+        size = C.c_size_t()
+        b._check(b._lib.itk_snapshot_to_itkv(b._h, self._h, model_fingerprint.encode(), None, 0, C.byref(size)))
+        buf = (C.c_uint8 * size.value)()
+        b._check(b._lib.itk_snapshot_to_itkv(b._h, self._h, model_fingerprint.encode(), buf, size.value, C.byref(size)))
+        return bytes(buf)
+
     def layer(self, layer: int):
         """(first_position, keys, values): the layer block ``[rows][Hkv][D]`` in the cache's element type
         (``float32`` or raw ``uint16`` half bits)."""
@@ -307,6 +316,13 @@ class CudaCompute:
     def install_prefix_snapshot(self, snapshot: DeviceSnapshot, slot: int = 0) -> int:
         self._check(self._lib.itk_snapshot_restore(self._h, slot, snapshot._h))
         return snapshot.token_count
+
+    def snapshot_from_itkv(self, data: bytes, expected_fingerprint: Optional[str] = None) -> DeviceSnapshot:
+        """Decode ``ITKV`` bytes (strictly), check geometry and fingerprint, and upload the rows."""
+        h = C.c_void_p()
+        fp = expected_fingerprint.encode() if expected_fingerprint is not None else None
+        self._check(self._lib.itk_snapshot_from_itkv(self._h, data, len(data), fp, C.byref(h)))
+        return DeviceSnapshot(self, h)
 
     def snapshot_from_host(self, token_count: int, blocks) -> DeviceSnapshot:
         """Build a device snapshot from f32 layer blocks ``[(first_position, keys, values)]`` laid out like the

@@ -191,3 +191,67 @@ def test_shared_prefix_snapshot_at_full_size_round_trips():
     out = gpu.attention_batch(9, list(range(sessions + 1)), [tokens] * (sessions + 1), 1, qb, kb, vb)
     out = out.reshape(sessions + 1, -1)
     assert np.abs(out - out[0]).max() <= 1e-5 * np.abs(out[0]).max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_itkv_bytes_equal_the_oracle_encoding_and_round_trip(dtype):
+    """crates/itak-kv/src/snapshot.rs:13-29, 381-540: the device snapshot's ITKV bytes equal, byte for byte, the
+    oracle's encoding of the same cache (wrapped ring layers included), and bytes produced by the oracle install the
+    oracle's state on the device."""
+    import struct
+
+    window, hkv, d, tokens = [4, 0, 4], 2, 8, 70
+    gpu, (ref,) = make_pair(window, 2, hkv, d, dtype=dtype, max_context=128, chunk_cap=64)
+    fill(gpu, ref, window, hkv, d, tokens, dtype, seed=21)
+    want = orc.KvSnapshot.capture(ref, "model-a").to_bytes()
+    got = gpu.capture_prefix_snapshot().to_itkv("model-a")
+    assert got == want
+    assert struct.unpack_from("<Q", got, len(got) - 8)[0] == orc.checksum(got[:-8])
+
+    other = CudaCompute(3, 2, hkv, d, n_slots=1, max_context=128, chunk_cap=64, kv_dtype=dtype, layer_window=window)
+    snap = other.snapshot_from_itkv(want, expected_fingerprint="model-a")
+    assert snap.token_count == tokens
+    other.install_prefix_snapshot(snap)
+    for layer in range(3):
+        assert_view_equal(other, ref, layer, dtype)
+    assert other.capture_prefix_snapshot().to_itkv("model-a") == want
+
+
+def test_itkv_decode_refusals_are_named():
+    """crates/itak-kv/src/snapshot.rs:709-813 and 345-371 on the device side's decoder."""
+    import struct
+
+    window, hkv, d = [4, 0], 2, 4
+    gpu, (ref,) = make_pair(window, 2, hkv, d, dtype=KvDtype.F32, max_context=32, chunk_cap=8)
+    fill(gpu, ref, window, hkv, d, 5, KvDtype.F32, seed=2)
+    good = gpu.capture_prefix_snapshot().to_itkv("model-a")
+
+    def refusal(data, fingerprint=None):
+        with pytest.raises(CudaComputeError) as e:
+            gpu.snapshot_from_itkv(data, fingerprint)
+        return e.value
+
+    flipped = bytearray(good)
+    flipped[len(good) - 12] ^= 0xFF
+    assert refusal(bytes(flipped)).code == _lib.ERR_CHECKSUM_MISMATCH
+    assert refusal(good[:8]).code == _lib.ERR_TRUNCATED
+    bad = bytearray(good)
+    bad[0] = ord("X")
+    assert refusal(bytes(bad)).code == _lib.ERR_BAD_MAGIC
+    v2 = bytearray(good)
+    v2[4] = 2
+    assert refusal(bytes(v2)).code == _lib.ERR_UNSUPPORTED_VERSION
+    e = refusal(good + b"\0")
+    assert e.code == _lib.ERR_INCONSISTENT_SNAPSHOT and "trailing" in e.msg
+    forged = b"ITKV" + struct.pack("<IIQIII", 1, 0, 0, 1, 1, 0xFFFFFFFF)
+    assert refusal(forged).code == _lib.ERR_INCONSISTENT_SNAPSHOT
+    overflow = b"ITKV" + struct.pack("<II", 1, 1) + b"x" + struct.pack("<QIII", 1 << 32, 65536, 65536, 1)
+    overflow += bytes(4) + struct.pack("<QQQ", 0, 0, 0)
+    overflow += struct.pack("<Q", orc.checksum(overflow))
+    assert refusal(overflow).code == _lib.ERR_INCONSISTENT_SNAPSHOT
+    assert refusal(good, "model-b").code == _lib.ERR_FINGERPRINT_MISMATCH
+    foreign = CudaCompute(2, 2, hkv, 8, n_slots=1, max_context=32, chunk_cap=8, kv_dtype=KvDtype.F32, layer_window=window)
+    with pytest.raises(CudaComputeError) as e:
+        foreign.snapshot_from_itkv(good, "model-a")
+    assert e.value.code == _lib.ERR_GEOMETRY_MISMATCH
+    gpu.snapshot_from_itkv(good, "model-a")
