@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--kv-heads", type=int, default=None, help="override the KV head count (shard studies)")
     ap.add_argument("--sequences", type=int, default=None, help="override the number of resident sequences")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer directly instead of replaying a CUDA graph")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="N > 1: gather the head outputs with an NCCL all-gather per layer instead of inside the kernel")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-units", type=int, default=None, help="(sequence, layer) units in the CPU sample")
@@ -298,6 +300,7 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    gather_info = {"kind": "NCCL all-gather per layer"} if world > 1 else None
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     prof_steps = 0
@@ -332,16 +335,32 @@ def run_ours(args):
         position += 1
         barrier()
         replays = args.warmup + args.steps
+        fused = world > 1 and not args.nccl_gather
+        slot_bytes = seqs * hq_l * d * 4
+        if fused:
+            # Every rank's gather buffer [layers][world][seqs][hq_l * d]; the decode kernel of rank r writes its
+            # rows into slot [layer][r] of every rank's buffer.
+            _, handle = be.gather_create(world, rank, layers * world * slot_bytes)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            for r in range(world):
+                be.gather_open(r, handles[r])
+            be.gather_reset()
+            barrier()
         be.resident_begin(slots, replays)
         graphs = []
         for i in range(pool):
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=stream):
                 for layer in range(layers):
-                    be.resident_layer(layer, q_in[i, layer].data_ptr(), k_in[i, layer].data_ptr(),
-                                      v_in[i, layer].data_ptr(), out[layer].data_ptr())
-                    if world > 1:
-                        dist.all_gather_into_tensor(gathered[layer], out[layer])
+                    if fused:
+                        be.resident_layer_gather(layer, q_in[i, layer].data_ptr(), k_in[i, layer].data_ptr(),
+                                                 v_in[i, layer].data_ptr(), (layer * world + rank) * slot_bytes)
+                    else:
+                        be.resident_layer(layer, q_in[i, layer].data_ptr(), k_in[i, layer].data_ptr(),
+                                          v_in[i, layer].data_ptr(), out[layer].data_ptr())
+                        if world > 1:
+                            dist.all_gather_into_tensor(gathered[layer], out[layer])
                 be.resident_advance()
             graphs.append(g)
         torch.cuda.set_stream(stream)
@@ -361,6 +380,9 @@ def run_ours(args):
         clocks = sampler.stop() if sampler else None
         be.resident_end(replays)
         position += replays
+        if fused:
+            gather_info = {"kind": "stores to peer memory from the decode kernel, flag per source rank",
+                           "waits_timed_out": be.gather_status()}
         launches = args.steps * (layers + 1)  # per rank: one fused kernel per layer plus the position advance
         del graphs, g
         # The same steps once more as direct launches with a CUDA-event pair around every kernel: the decode
@@ -452,7 +474,7 @@ def run_ours(args):
             "config": {"workload": args.workload, "layers": layers, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
                        "sequences": seqs, "context": ctx_first, "kv_dtype": "f16",
                        "launch": "direct" if args.no_graph else "cuda graph per step over device-side positions",
-                       "parallelism": f"kv-head shards x{world}" + (", NCCL all-gather per layer" if world > 1 else ""),
+                       "parallelism": f"kv-head shards x{world}", "gather": gather_info,
                        "l2": "inputs larger than L2: every layer streams its own KV, "
                              f"{bytes_launch_rank / 2**20:.0f} MiB per launch"},
             "kv_read_gbs": bytes_step_total / (ms_per_step * 1e-3) / 1e9,

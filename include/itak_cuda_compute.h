@@ -182,6 +182,24 @@ int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const f
 int itk_resident_advance(itk_backend* b);
 int itk_resident_end(itk_backend* b, uint64_t steps_done);
 
+/* The per-layer gather of head outputs across the GPUs of one box, done by the decode kernel itself (no
+ * counterpart in the reference, which is single-GPU).  Every rank owns a KV-head shard (a backend created with
+ * its share of the heads).  Each rank creates one gather buffer, the ranks exchange the 64-byte handles (any
+ * host channel) and open each other's; inside the replayable loop itk_resident_layer_gather then behaves like
+ * itk_resident_layer, except that the CTA finishing a (sequence, head) cell stores its rows - plain stores to
+ * peer-mapped memory over NVLink - at `gather_offset_bytes` of EVERY rank's buffer (the caller gives each rank
+ * and layer its own offset), and counts the cell on every rank's flag array.  Before a kernel of the loop uses
+ * its inputs it checks, with a bounded wait, that all ranks' cells of the previous launch have arrived
+ * (itk_gather_status reports a wait that ran out).  All ranks must call itk_gather_reset, then synchronise with
+ * each other, before itk_resident_begin; a step of the loop must launch every layer exactly once. */
+int itk_gather_create(itk_backend* b, uint32_t world, uint32_t rank, uint64_t data_bytes, void** local_data,
+                      uint8_t* handle64);
+int itk_gather_open(itk_backend* b, uint32_t peer_rank, const uint8_t* handle64);
+int itk_gather_reset(itk_backend* b);
+int itk_gather_status(itk_backend* b, uint32_t* error_bits);
+int itk_resident_layer_gather(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
+                              uint64_t gather_offset_bytes);
+
 /* gqa_attention alone (crates/attention/src/attention.rs:104-215) over what a
  * slot already holds: `rows` queries at query_positions[], host buffers.
  * Refuses ITK_ERR_NO_VISIBLE_KEYS when a query sees nothing. */

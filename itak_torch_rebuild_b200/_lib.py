@@ -96,6 +96,11 @@ SIGNATURES = {
     "itk_resident_layer": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "itk_resident_advance": (C.c_int, [_vp]),
     "itk_resident_end": (C.c_int, [_vp, _u64]),
+    "itk_gather_create": (C.c_int, [_vp, _u32, _u32, _u64, C.POINTER(_vp), _vp]),
+    "itk_gather_open": (C.c_int, [_vp, _u32, _vp]),
+    "itk_gather_reset": (C.c_int, [_vp]),
+    "itk_gather_status": (C.c_int, [_vp, _u32p]),
+    "itk_resident_layer_gather": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _u64]),
     "itk_gqa_attention": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _u32, _u64p, _vp]),
     "itk_append": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _u64]),
     "itk_append_rows": (C.c_int, [_vp, _u32, _u32, _vp, _vp, _u32, _u64]),

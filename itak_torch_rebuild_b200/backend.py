@@ -234,6 +234,30 @@ class CudaCompute:
     def resident_end(self, steps_done: int):
         self._check(self._lib.itk_resident_end(self._h, steps_done))
 
+    # -- gather fused into the decode kernel (multi-GPU) ------------------------------------------
+    def gather_create(self, world: int, rank: int, data_bytes: int):
+        """Allocate this rank's gather buffer; returns (device pointer of its data, 64-byte handle to send to peers)."""
+        ptr = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        self._check(self._lib.itk_gather_create(self._h, world, rank, data_bytes, C.byref(ptr), handle))
+        return ptr.value, bytes(handle)
+
+    def gather_open(self, peer_rank: int, handle: bytes):
+        buf = (C.c_uint8 * 64).from_buffer_copy(handle)
+        self._check(self._lib.itk_gather_open(self._h, peer_rank, buf))
+
+    def gather_reset(self):
+        self._check(self._lib.itk_gather_reset(self._h))
+
+    def gather_status(self) -> int:
+        bits = C.c_uint32()
+        self._check(self._lib.itk_gather_status(self._h, C.byref(bits)))
+        return bits.value
+
+    def resident_layer_gather(self, layer: int, q_ptr: int, k_ptr: int, v_ptr: int, gather_offset_bytes: int):
+        self._check(self._lib.itk_resident_layer_gather(self._h, layer, C.c_void_p(q_ptr), C.c_void_p(k_ptr),
+                                                        C.c_void_p(v_ptr), gather_offset_bytes))
+
     def gqa_attention(self, layer: int, q, query_positions: Sequence[int], slot: int = 0) -> np.ndarray:
         """``gqa_attention`` over what the slot already holds; one query row per listed position."""
         q = _host_f32(q).reshape(-1)

@@ -67,6 +67,24 @@ __device__ __forceinline__ void split_half(float x, __half& hi, __half& lo) {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Final-output stores: to AttnLaunch::out when set, and to every rank's gather buffer when the launch gathers.
+__device__ __forceinline__ void store_out(const AttnLaunch& p, size_t off, float v) {
+    if (p.out) p.out[off] = v;
+    for (uint32_t j = 0; j < p.gather.n_peers; ++j) p.gather.peer_out[j][off] = v;
+}
+__device__ __forceinline__ void store_out4(const AttnLaunch& p, size_t off4, float4 v) {
+    if (p.out) reinterpret_cast<float4*>(p.out)[off4] = v;
+    for (uint32_t j = 0; j < p.gather.n_peers; ++j) reinterpret_cast<float4*>(p.gather.peer_out[j])[off4] = v;
+}
+// After a cell's output went out: make it visible system-wide, then count it on every rank.
+__device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p) {
+    if (p.gather.n_peers == 0) return;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (uint32_t j = 0; j < p.gather.n_peers; ++j) atomicAdd_system(p.gather.peer_flags[j] + p.gather.my_rank, 1u);
+}
+
 constexpr int kMaxSplits = 256;  // upper bound on the partials merged for one cell (sizes the merge scratch)
 
 // CTA epilogue for one cell = (unit, head chunk).  On entry the CTA's own result
@@ -88,12 +106,13 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
                                             const float* fm, const float* fl, int* s_flag, float* wscratch) {
     const uint32_t tid = threadIdx.x;
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
-    float* out = p.out + (static_cast<size_t>(unit) * p.q_heads + head0) * D;
+    const size_t out_off = (static_cast<size_t>(unit) * p.q_heads + head0) * D;  // element offset of the cell's rows
     if (n_parts == 1) {
         for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
             const uint32_t h = idx / D;
-            out[idx] = fo[idx] / fl[h];
+            store_out(p, out_off + idx, fo[idx] / fl[h]);
         }
+        signal_cell_delivered(p);
         return;
     }
     const size_t cell = static_cast<size_t>(unit) * HY + hy;
@@ -148,7 +167,6 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
         const uint32_t cols = nh * D / 4;
         const size_t pstride = kHeadsPerCta * D / 4;  // float4s per part
         const float4* src4 = reinterpret_cast<const float4*>(all_o);
-        float4* out4 = reinterpret_cast<float4*>(out);
         for (uint32_t c0 = tid; c0 < cols; c0 += 2 * THREADS) {
             const uint32_t c1 = c0 + THREADS;
             const bool two = c1 < cols;
@@ -172,8 +190,8 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
                 }
             }
             const float i0 = inv_l[h0], i1 = inv_l[h1];
-            out4[c0] = make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0);
-            if (two) out4[c1] = make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1);
+            store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
+            if (two) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
         }
     } else {
         for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
@@ -182,9 +200,10 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
             float acc = 0.f;
             for (uint32_t s = 0; s < n_parts; ++s)
                 acc += w_m[s * kHeadsPerCta + h] * __ldcg(src + static_cast<size_t>(s) * (kHeadsPerCta * D));
-            out[idx] = acc * inv_l[h];
+            store_out(p, out_off + idx, acc * inv_l[h]);
         }
     }
+    signal_cell_delivered(p);
     if (tid == 0) p.tickets[cell] = 0u;
 }
 

@@ -98,6 +98,13 @@ struct itk_backend {
     std::vector<uint32_t> res_slots;
     uint64_t res_max_steps = 0;
     uint32_t res_ctas = 0, res_parts = 0;
+    uint32_t res_launches_in_step = 0;
+    // fused gather: one allocation per rank = [256-byte header: flags[8], err @64, base_pos @128][data]
+    unsigned char* gth_local = nullptr;
+    unsigned char* gth_peer[itk::kMaxPeers] = {};
+    uint32_t gth_world = 0, gth_rank = 0;
+    uint64_t gth_bytes = 0;
+    bool gth_wait = true;  // ITK_GATHER_WAIT=0: do not check the peers' previous launch at kernel start
     int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
     bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
@@ -543,6 +550,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     for (uint32_t s = 0; s < cfg->n_slots; ++s) drop_slot(b, s);
     if (const char* env = std::getenv("ITK_DECODE_SPLITS")) b->forced_splits = std::atoi(env);
     if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
+    if (const char* env = std::getenv("ITK_GATHER_WAIT")) b->gth_wait = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
@@ -565,6 +573,9 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->d_out);
     cudaFree(b->gather_buf);
     cudaFree(b->d_states);
+    for (uint32_t j = 0; j < itk::kMaxPeers; ++j)
+        if (b->gth_peer[j] && j != b->gth_rank) cudaIpcCloseMemHandle(b->gth_peer[j]);
+    cudaFree(b->gth_local);
     for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
     if (b->own_stream) cudaStreamDestroy(b->own_stream);
     delete b;
@@ -666,12 +677,17 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
     b->res_ctas = static_cast<uint32_t>(ctas);
     b->res_parts = static_cast<uint32_t>(cap);
     b->res_prev_layer = -1;
+    b->res_launches_in_step = 0;
+    if (b->gth_local) {
+        ITK_CUDA(b, cudaMemcpyAsync(b->gth_local + 128, &states[0].pos, sizeof(uint32_t), cudaMemcpyHostToDevice, b->stream),
+                 "gather base position upload");
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather base position upload");
+    }
     return ITK_OK;
 }
 
-int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
-                       float* d_out) {
-    if (!b || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
+                               float* d_out, bool gather, uint64_t gather_offset_bytes) {
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
     if (int rc = check_layer(b, layer)) return rc;
     AttnLaunch p{};
@@ -690,12 +706,105 @@ int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const f
     p.k_new = d_k;
     p.v_new = d_v;
     p.seq_dev = b->d_states;
+    if (gather) {
+        if (!b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: no gather buffer (itk_gather_create)");
+        const uint64_t slot_bytes = static_cast<uint64_t>(p.n_seqs) * b->q_width() * sizeof(float);
+        if (gather_offset_bytes % 16 != 0 || gather_offset_bytes + slot_bytes > b->gth_bytes)
+            return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: offset " + zu(gather_offset_bytes) +
+                                                         " is misaligned or past the buffer of " + zu(b->gth_bytes) + " bytes");
+        p.gather.n_peers = b->gth_world;
+        p.gather.my_rank = b->gth_rank;
+        for (uint32_t j = 0; j < b->gth_world; ++j) {
+            if (!b->gth_peer[j]) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: rank " + zu(j) + " is not open");
+            p.gather.peer_out[j] = reinterpret_cast<float*>(b->gth_peer[j] + 256 + gather_offset_bytes);
+            p.gather.peer_flags[j] = reinterpret_cast<unsigned int*>(b->gth_peer[j]);
+        }
+        p.gather.my_flags = reinterpret_cast<const unsigned int*>(b->gth_local);
+        p.gather.err = reinterpret_cast<unsigned int*>(b->gth_local + 64);
+        p.gather.base_pos = reinterpret_cast<const uint32_t*>(b->gth_local + 128);
+        p.gather.launches_per_step = b->cfg.n_layers;
+        p.gather.launches_before = b->res_launches_in_step;
+        p.gather.cells = p.n_seqs * b->cfg.kv_heads * b->gchunks;
+        p.gather.wait_prev = b->gth_wait ? 1u : 0u;
+    }
     // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
     // the same layer) the kernel waits first.
     p.pdl = !b->use_pdl ? 0u : ((b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer) ? 2u : 1u);
     ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
              "resident decode launch");
     b->res_prev_layer = static_cast<int>(layer);
+    b->res_launches_in_step += 1;
+    return ITK_OK;
+}
+
+int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
+                       float* d_out) {
+    if (!b || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+    return resident_layer_impl(b, layer, d_q, d_k, d_v, d_out, false, 0);
+}
+
+int itk_resident_layer_gather(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
+                              uint64_t gather_offset_bytes) {
+    if (!b || !d_q || !d_k || !d_v) return ITK_ERR_INVALID_ARGUMENT;
+    return resident_layer_impl(b, layer, d_q, d_k, d_v, nullptr, true, gather_offset_bytes);
+}
+
+int itk_gather_create(itk_backend* b, uint32_t world, uint32_t rank, uint64_t data_bytes, void** local_data,
+                      uint8_t* handle64) {
+    if (!b || !local_data || !handle64) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: buffer already created");
+    if (world < 1 || world > itk::kMaxPeers || rank >= world || data_bytes == 0)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: 1..8 ranks, rank < world, non-empty buffer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* ptr = nullptr;
+    ITK_CUDA(b, cudaMalloc(&ptr, 256 + data_bytes), "gather buffer allocation");
+    ITK_CUDA(b, cudaMemset(ptr, 0, 256 + data_bytes), "gather buffer clear");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) {
+        cudaFree(ptr);
+        return b->cuda_fail(e, "cudaIpcGetMemHandle");
+    }
+    std::memcpy(handle64, &h, 64);
+    b->gth_local = static_cast<unsigned char*>(ptr);
+    b->gth_world = world;
+    b->gth_rank = rank;
+    b->gth_bytes = data_bytes;
+    b->gth_peer[rank] = b->gth_local;
+    *local_data = b->gth_local + 256;
+    return ITK_OK;
+}
+
+int itk_gather_open(itk_backend* b, uint32_t peer_rank, const uint8_t* handle64) {
+    if (!b || !handle64) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (!b->gth_local || peer_rank >= b->gth_world)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: create the local buffer first; rank must be < world");
+    if (peer_rank == b->gth_rank || b->gth_peer[peer_rank]) return ITK_OK;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, 64);
+    void* ptr = nullptr;
+    ITK_CUDA(b, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+    b->gth_peer[peer_rank] = static_cast<unsigned char*>(ptr);
+    return ITK_OK;
+}
+
+int itk_gather_reset(itk_backend* b) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (!b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: no gather buffer");
+    ITK_CUDA(b, cudaMemsetAsync(b->gth_local, 0, 128, b->stream), "gather flag clear");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather flag clear");
+    return ITK_OK;
+}
+
+int itk_gather_status(itk_backend* b, uint32_t* error_bits) {
+    if (!b || !error_bits) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (!b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: no gather buffer");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather status");
+    ITK_CUDA(b, cudaMemcpy(error_bits, b->gth_local + 64, sizeof(uint32_t), cudaMemcpyDeviceToHost), "gather status");
     return ITK_OK;
 }
 
@@ -705,6 +814,7 @@ int itk_resident_advance(itk_backend* b) {
     ITK_CUDA(b, itk::launch_advance_states(b->d_states, static_cast<uint32_t>(b->res_slots.size()), b->stream,
                                            &b->stats.kernel_launches), "state advance launch");
     b->res_prev_layer = -1;
+    b->res_launches_in_step = 0;
     return ITK_OK;
 }
 

@@ -50,6 +50,26 @@ struct LayerView {
     uint32_t head_dim;
 };
 
+constexpr int kMaxPeers = 8;  // GPUs of one box
+
+// The per-layer gather of head outputs done by the decode kernel itself: the CTA that writes a cell's final
+// output stores it into the same place of every rank's gather buffer (plain stores to peer-mapped memory over
+// NVLink) and then bumps entry [my_rank] of every rank's flag array, so a consumer on rank j knows that rank r has
+// delivered c cells once flags_j[r] >= c.
+struct GatherTarget {
+    uint32_t n_peers;                    // 0 = outputs go to AttnLaunch::out only
+    uint32_t my_rank;
+    float* peer_out[kMaxPeers];          // this rank's [n_seqs][q_heads][D] slot inside every rank's buffer
+    unsigned int* peer_flags[kMaxPeers]; // every rank's flag array (kMaxPeers entries)
+    const unsigned int* my_flags;        // the local flag array, written by the peers
+    unsigned int* err;                   // local word: bit 0 = a bounded wait ran out
+    const uint32_t* base_pos;            // device word: position of sequence 0 when the loop began
+    uint32_t launches_per_step;          // decode launches of one step of the loop
+    uint32_t launches_before;            // decode launches of this step that precede this one
+    uint32_t cells;                      // cells every rank delivers per launch
+    uint32_t wait_prev;                  // 1 = before using its inputs, check that every peer's previous launch arrived
+};
+
 struct AttnLaunch {
     LayerView layer;
     const float* q;          // [n_seqs][rows][q_heads][D]
@@ -70,6 +90,7 @@ struct AttnLaunch {
     uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
+    GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
     float scale;             // score scale, 1/sqrt(D) by default
