@@ -45,7 +45,8 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5_long_context_decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5_long_context_decode",
+                    choices=sorted(WORKLOADS) + ["c4_prefix_restore", "c4_spec_verify"])
     ap.add_argument("--context", type=int, default=None, help="override the context length (smoke runs)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (smoke runs)")
     ap.add_argument("--q-heads", type=int, default=None, help="override the query head count (shard studies)")
@@ -494,7 +495,16 @@ def run_ours(args):
 
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.workload in ("c4_prefix_restore", "c4_spec_verify"):
+        # the path's other rows, one GPU, measured by bench_paths.py in the same JSON shape
+        import bench_paths
+
+        if args.impl == "reference" or args.gpus != 1:
+            print(json.dumps({"impl": args.impl, "unavailable": "this workload is measured on one GPU, CUDA arm only"}))
+            return
+        (bench_paths.run_prefix_restore if args.workload == "c4_prefix_restore" else bench_paths.run_spec_verify)(
+            args, ClockSampler)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

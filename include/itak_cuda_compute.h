@@ -139,6 +139,8 @@ int itk_get_stats(const itk_backend* b, itk_stats* out);
 int itk_profile_enable(itk_backend* b, uint32_t capacity);
 int itk_profile_read(itk_backend* b, double* attention_ms, uint64_t* attention_launches, double* append_ms,
                      uint64_t* append_launches);
+/* The snapshot gather / restore scatter launches summed by the last itk_profile_read. */
+int itk_profile_read_copy(itk_backend* b, double* copy_ms, uint64_t* copy_launches);
 
 /* ---- the attention step ---------------------------------------------------- */
 

@@ -106,6 +106,7 @@ SIGNATURES = {
     "itk_append_rows": (C.c_int, [_vp, _u32, _u32, _vp, _vp, _u32, _u64]),
     "itk_append_rows_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp]),
     "itk_profile_enable": (C.c_int, [_vp, _u32]),
+    "itk_profile_read_copy": (C.c_int, [_vp, C.POINTER(C.c_double), _u64p]),
     "itk_profile_read": (C.c_int, [_vp, C.POINTER(C.c_double), _u64p, C.POINTER(C.c_double), _u64p]),
     "itk_next_position": (C.c_int, [_vp, _u32, _u32, _u64p]),
     "itk_stored_len": (C.c_int, [_vp, _u32, _u32, _u64p]),

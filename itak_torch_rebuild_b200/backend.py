@@ -182,8 +182,10 @@ class CudaCompute:
         a_ms, p_ms = C.c_double(), C.c_double()
         a_n, p_n = C.c_uint64(), C.c_uint64()
         self._check(self._lib.itk_profile_read(self._h, C.byref(a_ms), C.byref(a_n), C.byref(p_ms), C.byref(p_n)))
+        c_ms, c_n = C.c_double(), C.c_uint64()
+        self._check(self._lib.itk_profile_read_copy(self._h, C.byref(c_ms), C.byref(c_n)))
         return {"attention_ms": a_ms.value, "attention_launches": a_n.value, "append_ms": p_ms.value,
-                "append_launches": p_n.value}
+                "append_launches": p_n.value, "copy_ms": c_ms.value, "copy_launches": c_n.value}
 
     # -- Compute::attention ---------------------------------------------------------------
     def attention(self, layer: int, q, k, v, cache: PositionCache, slot: int = 0) -> np.ndarray:

@@ -81,8 +81,10 @@ __device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p) {
     if (p.gather.n_peers == 0) return;
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0)
-        for (uint32_t j = 0; j < p.gather.n_peers; ++j) atomicAdd_system(p.gather.peer_flags[j] + p.gather.my_rank, 1u);
+    // one thread per peer, and a reduction (no value comes back, so nothing waits for the NVLink round trip)
+    if (threadIdx.x < p.gather.n_peers)
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[threadIdx.x] + p.gather.my_rank)
+                     : "memory");
 }
 
 constexpr int kMaxSplits = 256;  // upper bound on the partials merged for one cell (sizes the merge scratch)

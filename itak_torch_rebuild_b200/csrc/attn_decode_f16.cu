@@ -212,18 +212,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     // peers' previous launch has arrived here.  The wait is bounded; if it runs out the kernel records that and
     // carries on (its own arithmetic does not depend on the gathered data).
     if (p.gather.n_peers != 0 && p.gather.wait_prev != 0) {
-        if (tid == 0) {
+        if (static_cast<uint32_t>(tid) < p.gather.n_peers) {  // one polling thread per source rank
             const uint32_t steps_done = seq_of(p, 0).q_pos0 - *p.gather.base_pos;
             const uint32_t target = (steps_done * p.gather.launches_per_step + p.gather.launches_before) * p.gather.cells;
-            for (uint32_t j = 0; j < p.gather.n_peers; ++j) {
-                uint32_t seen = 0, spins = 0;
-                for (;;) {
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(p.gather.my_flags + j) : "memory");
-                    if (seen >= target) break;
-                    if (++spins > 200000u) {
-                        atomicOr(p.gather.err, 1u);
-                        break;
-                    }
+            uint32_t seen = 0, spins = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(p.gather.my_flags + tid) : "memory");
+                if (seen >= target) break;
+                if (++spins > 200000u) {
+                    atomicOr(p.gather.err, 1u);
+                    break;
                 }
             }
         }

@@ -107,10 +107,12 @@ struct itk_backend {
     bool gth_wait = true;  // ITK_GATHER_WAIT=0: do not check the peers' previous launch at kernel start
     int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
     bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
-    // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append
+    // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append, 2 = snapshot gather / restore scatter
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
     size_t prof_used = 0;
+    double prof_copy_ms = 0.0;
+    uint64_t prof_copy_launches = 0;
 
     int fail(int code, std::string msg) const {
         err = std::move(msg);
@@ -417,10 +419,12 @@ int run_copy(itk_backend* b, uint32_t slot, void* snap_base, const std::vector<u
             p.layer[i].ring = b->ring[l];
             p.layer[i].first_pos = static_cast<uint32_t>(first[at + i]);
             p.layer[i].rows = static_cast<uint32_t>(rows[at + i]);
-            p.vec_prefix[i + 1] = p.vec_prefix[i] + rows[at + i] * units_per_row;
+            p.vec_prefix[i + 1] = p.vec_prefix[i] + ((rows[at + i] + 7) / 8) * units_per_row;  // 8-row work items
         }
         p.total_vec = 2 * p.vec_prefix[m];
+        const long ev = prof_begin(b, 2);
         ITK_CUDA(b, itk::launch_snapshot_copy(p, b->stream, &b->stats.kernel_launches), "snapshot copy launch");
+        prof_end(b, ev);
     }
     return ITK_OK;
 }
@@ -855,8 +859,8 @@ int itk_profile_read(itk_backend* b, double* attention_ms, uint64_t* attention_l
     if (!b) return ITK_ERR_INVALID_ARGUMENT;
     cudaSetDevice(b->cfg.device);
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "profile read");
-    double ms[2] = {0.0, 0.0};
-    uint64_t n[2] = {0, 0};
+    double ms[3] = {0.0, 0.0, 0.0};
+    uint64_t n[3] = {0, 0, 0};
     for (size_t at = 0; at + 1 < b->prof_used; at += 2) {
         float t = 0.f;
         ITK_CUDA(b, cudaEventElapsedTime(&t, b->prof_events[at], b->prof_events[at + 1]), "profile read");
@@ -868,7 +872,16 @@ int itk_profile_read(itk_backend* b, double* attention_ms, uint64_t* attention_l
     if (attention_launches) *attention_launches = n[0];
     if (append_ms) *append_ms = ms[1];
     if (append_launches) *append_launches = n[1];
+    b->prof_copy_ms = ms[2];
+    b->prof_copy_launches = n[2];
     b->prof_used = 0;
+    return ITK_OK;
+}
+
+int itk_profile_read_copy(itk_backend* b, double* copy_ms, uint64_t* copy_launches) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    if (copy_ms) *copy_ms = b->prof_copy_ms;
+    if (copy_launches) *copy_launches = b->prof_copy_launches;
     return ITK_OK;
 }
 

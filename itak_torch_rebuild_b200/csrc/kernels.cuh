@@ -124,8 +124,8 @@ struct CopyLaunch {
     uint32_t slot, kv_heads, head_dim, n_layers;
     uint32_t elem_bytes;
     uint32_t to_snapshot;  // 1 = gather slab -> snapshot, 0 = scatter snapshot -> slab
-    unsigned long long total_vec;  // 16-byte vectors over all layers (K and V)
-    unsigned long long vec_prefix[kMaxLayersPerLaunch + 1];  // running K-vector counts per layer
+    unsigned long long total_vec;  // work items over all layers, K and V (an item = 8 rows of one vector column)
+    unsigned long long vec_prefix[kMaxLayersPerLaunch + 1];  // running K work-item counts per layer
     CopyLayer layer[kMaxLayersPerLaunch];
 };
 

@@ -70,13 +70,29 @@ __global__ void __launch_bounds__(256) convert_kernel(const float* src, void* ds
 // layer's visible rows in absolute-position order, `[rows][kv_heads][D]` for K
 // then V (crates/itak-kv/src/snapshot.rs:247-302); the device rows live at
 // position % ring, so the stored range maps to at most two storage runs
-// (crates/wgpu-compute/src/session.rs:320-346) - here resolved per vector.
-// VB = bytes moved per thread step: 16 when a head row is a multiple of 16
-// bytes, else one element.
+// (crates/wgpu-compute/src/session.rs:320-346) - here resolved per row.
+// VB = bytes moved per access: 16 when a head row is a multiple of 16 bytes,
+// else one element.  A work item is (layer, K or V, block of kCopyRows rows,
+// head, vector): its index arithmetic is done once and kCopyRows loads are in
+// flight per thread; lanes run over the vectors of a head row, so a warp
+// reads and writes whole 256-byte head rows.
+constexpr uint32_t kCopyRows = 8;
+
+template <int VB>
+struct CopyVec;
+template <>
+struct CopyVec<16> { using type = uint4; };
+template <>
+struct CopyVec<4> { using type = uint32_t; };
+template <>
+struct CopyVec<2> { using type = unsigned short; };
+
 template <int VB>
 __global__ void __launch_bounds__(256) snapshot_copy_kernel(const __grid_constant__ CopyLaunch p) {
+    using V = typename CopyVec<VB>::type;
     const uint32_t row_units = p.head_dim * p.elem_bytes / VB;  // vectors per (row, head)
     const unsigned long long total_k = p.vec_prefix[p.n_layers];
+    const unsigned long long row_bytes = static_cast<unsigned long long>(p.head_dim) * p.elem_bytes;
     for (unsigned long long idx = blockIdx.x * static_cast<unsigned long long>(blockDim.x) + threadIdx.x;
          idx < p.total_vec; idx += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
         const bool is_v = idx >= total_k;
@@ -88,29 +104,44 @@ __global__ void __launch_bounds__(256) snapshot_copy_kernel(const __grid_constan
             if (p.vec_prefix[mid] <= j) lo = mid; else hi = mid;
         }
         const CopyLayer L = p.layer[lo];
-        // a layer block holds fewer than 2^32 vectors (the launcher checks), so 32-bit divides suffice
+        // a layer holds fewer than 2^32 work items (the launcher checks), so 32-bit divides suffice
         uint32_t w = static_cast<uint32_t>(j - p.vec_prefix[lo]);
         const uint32_t u = w % row_units;
         w /= row_units;
         const uint32_t h = w % p.kv_heads;
-        const uint32_t r = w / p.kv_heads;
-        const uint32_t srow = (L.first_pos + r) % L.ring;
-        const unsigned long long slab_elem =
-            L.slab_off + ((static_cast<unsigned long long>(p.slot) * p.kv_heads + h) * L.ring + srow) * p.head_dim;
-        const unsigned long long snap_elem =
-            (is_v ? L.snap_v : L.snap_k) + (static_cast<unsigned long long>(r) * p.kv_heads + h) * p.head_dim;
-        unsigned char* slab = static_cast<unsigned char*>(is_v ? p.v_slab : p.k_slab) + slab_elem * p.elem_bytes +
+        const uint32_t r0 = (w / p.kv_heads) * kCopyRows;
+        const uint32_t nr = min(kCopyRows, L.rows - r0);
+        uint32_t srow = (L.first_pos + r0) % L.ring;
+        unsigned char* slab = static_cast<unsigned char*>(is_v ? p.v_slab : p.k_slab) +
+                              (L.slab_off + (static_cast<unsigned long long>(p.slot) * p.kv_heads + h) * L.ring * p.head_dim) *
+                                  p.elem_bytes +
                               static_cast<unsigned long long>(u) * VB;
-        unsigned char* snap = static_cast<unsigned char*>(p.snap) + snap_elem * p.elem_bytes +
+        unsigned char* snap = static_cast<unsigned char*>(p.snap) +
+                              ((is_v ? L.snap_v : L.snap_k) +
+                               (static_cast<unsigned long long>(r0) * p.kv_heads + h) * p.head_dim) * p.elem_bytes +
                               static_cast<unsigned long long>(u) * VB;
-        unsigned char* dst = p.to_snapshot ? snap : slab;
-        const unsigned char* src = p.to_snapshot ? slab : snap;
-        if constexpr (VB == 16) {
-            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-        } else if constexpr (VB == 4) {
-            *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+        const unsigned long long snap_step = row_bytes * p.kv_heads;
+        V vals[kCopyRows];
+        uint32_t srows[kCopyRows];
+#pragma unroll
+        for (uint32_t i = 0; i < kCopyRows; ++i) {
+            srows[i] = srow;
+            if (++srow == L.ring) srow = 0;
+        }
+        if (p.to_snapshot) {
+#pragma unroll
+            for (uint32_t i = 0; i < kCopyRows; ++i)
+                if (i < nr) vals[i] = *reinterpret_cast<const V*>(slab + srows[i] * row_bytes);
+#pragma unroll
+            for (uint32_t i = 0; i < kCopyRows; ++i)
+                if (i < nr) *reinterpret_cast<V*>(snap + i * snap_step) = vals[i];
         } else {
-            *reinterpret_cast<unsigned short*>(dst) = *reinterpret_cast<const unsigned short*>(src);
+#pragma unroll
+            for (uint32_t i = 0; i < kCopyRows; ++i)
+                if (i < nr) vals[i] = *reinterpret_cast<const V*>(snap + i * snap_step);
+#pragma unroll
+            for (uint32_t i = 0; i < kCopyRows; ++i)
+                if (i < nr) *reinterpret_cast<V*>(slab + srows[i] * row_bytes) = vals[i];
         }
     }
 }
