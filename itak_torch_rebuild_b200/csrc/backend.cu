@@ -23,6 +23,7 @@
 namespace itk {
 cudaError_t configure_decode_f16();
 cudaError_t configure_verify_f16();
+cudaError_t configure_verify_tc();
 uint32_t verify_pair_chunks(uint32_t rows, uint32_t group);
 }
 
@@ -92,6 +93,10 @@ struct itk_backend {
     int forced_ctas = 0;         // ITK_DECODE_CTAS: persistent CTAs of the decode kernel (default 2 per SM)
     bool separate_append = false;  // ITK_SEPARATE_APPEND=1: decode steps launch the append kernel separately
     bool force_general = false;  // ITK_FORCE_GENERAL=1: multi-row launches take the CUDA-core kernel (A/B checks)
+    bool verify_tc = true;       // ITK_VERIFY_TC=0: multi-row launches take the mma.sync kernel instead of tcgen05
+    unsigned int* d_status = nullptr;  // device word kernels OR error bits into
+    unsigned int* h_status = nullptr;  // pinned host copy read after a synchronisation
+    bool status_pending = false;       // a kernel that can raise d_status was launched since the last check
     // resident decode loop (device-side sequence states, replayable)
     itk::SeqState* d_states = nullptr;
     bool res_active = false;
@@ -153,7 +158,8 @@ int check_layer(const itk_backend* b, uint32_t layer) {
 
 // KV splits for a decode launch: minimise waves x (tiles per CTA + fixed cost)
 // over the CTA slots the device offers (2 resident CTAs per SM).
-uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uint32_t tile, uint64_t scratch_mult = 1) {
+uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uint32_t tile, uint64_t scratch_mult = 1,
+                       uint32_t ctas_per_sm = 2) {
     if (b->forced_splits > 0) {
         uint64_t s = static_cast<uint64_t>(b->forced_splits);
         const uint64_t by_len = (n_max + tile - 1) / tile;
@@ -162,7 +168,7 @@ uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uin
         if (s > 256) s = 256;
         return static_cast<uint32_t>(s < 1 ? 1 : s);
     }
-    const uint64_t slots = static_cast<uint64_t>(b->sm_count) * 2;
+    const uint64_t slots = static_cast<uint64_t>(b->sm_count) * ctas_per_sm;
     uint64_t max_s = (n_max + 4 * tile - 1) / (4 * tile);  // at least four tiles per CTA
     if (max_s < 1) max_s = 1;
     if (max_s > 256) max_s = 256;
@@ -230,6 +236,22 @@ int run_append(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, 
     return ITK_OK;
 }
 
+// The kernels' error word: queued for download before a synchronisation that follows a launch able to raise it,
+// and turned into a named refusal afterwards (the word is cleared so that later calls start clean).
+void queue_status_read(itk_backend* b) {
+    if (b->status_pending)
+        cudaMemcpyAsync(b->h_status, b->d_status, sizeof(unsigned int), cudaMemcpyDeviceToHost, b->stream);
+}
+int check_status(itk_backend* b) {
+    if (!b->status_pending) return ITK_OK;
+    b->status_pending = false;
+    if (*b->h_status == 0u) return ITK_OK;
+    *b->h_status = 0u;
+    cudaMemsetAsync(b->d_status, 0, sizeof(unsigned int), b->stream);
+    return b->fail(ITK_ERR_CUDA, "a bounded wait on the tensor core ran out in the multi-row attention kernel; "
+                                 "the launch's outputs are not valid");
+}
+
 // Launch attention for `n` sequences of `rows` rows each (device q / out).
 // `d_k_new` / `d_v_new` (device f32 [n][kv_heads*D], may be null): the step's new rows for the decode kernel to
 // store itself; only honoured when the decode kernel takes the launch (see decode_fuses_append).
@@ -238,7 +260,10 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
     const uint32_t D = b->cfg.head_dim;
     const uint32_t HY = b->cfg.kv_heads * b->gchunks;
     const bool decode = b->f16 && itk::decode_f16_supported(D, rows);
-    const bool verify = b->f16 && !decode && !b->force_general && itk::verify_f16_supported(D, rows, b->group);
+    const bool verify_tc = b->f16 && !decode && !b->force_general && b->verify_tc &&
+                           itk::verify_tc_supported(D, rows, b->group);
+    const bool verify = !verify_tc && b->f16 && !decode && !b->force_general &&
+                        itk::verify_f16_supported(D, rows, b->group);
     // grid.z carries n_seqs * rows (general kernel) and is limited to 65535
     uint32_t per_launch = itk::kMaxSeqsPerLaunch;
     while (per_launch > 1 && static_cast<uint64_t>(per_launch) * rows > 65535) per_launch >>= 1;
@@ -253,6 +278,7 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
         p.part_o = b->part_o;
         p.part_ml = b->part_ml;
         p.tickets = b->tickets;
+        p.status = b->d_status;
         p.q_heads = b->cfg.q_heads;
         p.group = b->group;
         p.gchunks = b->gchunks;
@@ -269,8 +295,9 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
         // A "cell" is one (unit, head chunk) whose splits are merged: a (sequence, row) for the decode and
         // general kernels, a (sequence, block of 32 row-head pairs) for the verify kernel, which needs four
         // times the scratch per (cell, split).
-        const uint64_t cells = verify ? static_cast<uint64_t>(m) * HY * itk::verify_pair_chunks(rows, b->group)
-                                      : static_cast<uint64_t>(m) * rows * HY;
+        const uint64_t cells = verify_tc ? static_cast<uint64_t>(m) * HY * itk::verify_tc_pair_chunks(rows, b->group)
+                               : verify  ? static_cast<uint64_t>(m) * HY * itk::verify_pair_chunks(rows, b->group)
+                                         : static_cast<uint64_t>(m) * rows * HY;
         if (cells > b->ticket_cells)
             return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(cells) + " (row, head) cells exceed the scratch of " +
                                                  zu(b->ticket_cells));
@@ -290,6 +317,15 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                                                &b->stats.kernel_launches, &parts),
                      "decode attention launch");
             b->stats.last_splits = parts;
+            prof_end(b, ev);
+            continue;
+        }
+        if (verify_tc) {
+            // one CTA per SM; a partial slot holds verify_tc_pairs_per_cta rows instead of 8
+            p.splits = choose_splits(b, cells, n_max, 64, itk::verify_tc_pairs_per_cta(rows, b->group) / 8, 1);
+            b->stats.last_splits = p.splits;
+            b->status_pending = true;
+            ITK_CUDA(b, itk::launch_verify_tc(p, b->stream, &b->stats.kernel_launches), "tensor-core attention launch");
             prof_end(b, ev);
             continue;
         }
@@ -514,6 +550,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     b->sm_count = prop.multiProcessorCount;
     e = itk::configure_decode_f16();
     if (e == cudaSuccess) e = itk::configure_verify_f16();
+    if (e == cudaSuccess) e = itk::configure_verify_tc();
     if (e != cudaSuccess) return cuda_refuse(e, "kernel attribute setup");
     e = cudaStreamCreateWithFlags(&b->own_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) return cuda_refuse(e, "cudaStreamCreate");
@@ -548,6 +585,11 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (e != cudaSuccess) return cuda_refuse(e, "staging allocation");
     e = cudaMalloc(&b->d_states, itk::kMaxSeqsPerLaunch * sizeof(itk::SeqState));
     if (e != cudaSuccess) return cuda_refuse(e, "sequence-state allocation");
+    e = cudaMalloc(&b->d_status, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMallocHost(&b->h_status, sizeof(unsigned int));
+    if (e != cudaSuccess) return cuda_refuse(e, "status word allocation");
+    *b->h_status = 0u;
+    cudaMemsetAsync(b->d_status, 0, sizeof(unsigned int), b->stream);
     e = cudaStreamSynchronize(b->stream);
     if (e != cudaSuccess) return cuda_refuse(e, "initialisation");
     b->slots.resize(cfg->n_slots);
@@ -558,6 +600,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
+    if (const char* env = std::getenv("ITK_VERIFY_TC")) b->verify_tc = std::atoi(env) != 0;
     *out = b;
     return ITK_OK;
 }
@@ -577,6 +620,8 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->d_out);
     cudaFree(b->gather_buf);
     cudaFree(b->d_states);
+    cudaFree(b->d_status);
+    if (b->h_status) cudaFreeHost(b->h_status);
     for (uint32_t j = 0; j < itk::kMaxPeers; ++j)
         if (b->gth_peer[j] && j != b->gth_rank) cudaIpcCloseMemHandle(b->gth_peer[j]);
     cudaFree(b->gth_local);
@@ -595,8 +640,10 @@ int itk_set_stream(itk_backend* b, void* cuda_stream) {
 
 int itk_synchronize(itk_backend* b) {
     if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    queue_status_read(b);
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "synchronize");
-    return ITK_OK;
+    return check_status(b);
 }
 
 int itk_get_stats(const itk_backend* b, itk_stats* out) {
@@ -910,8 +957,9 @@ int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const u
     ITK_CUDA(b, cudaMemcpyAsync(b->d_q, q, qb, cudaMemcpyHostToDevice, b->stream), "q upload");
     if (int rc = step_device(b, layer, n_seqs, slots, positions, rows, b->d_q, b->d_k, b->d_v, b->d_out)) return rc;
     ITK_CUDA(b, cudaMemcpyAsync(out, b->d_out, qb, cudaMemcpyDeviceToHost, b->stream), "output download");
+    queue_status_read(b);
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention");
-    return ITK_OK;
+    return check_status(b);
 }
 
 int itk_attention(itk_backend* b, uint32_t slot, uint32_t layer, const float* q, size_t q_len, const float* k,

@@ -93,6 +93,8 @@ struct AttnLaunch {
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
+    unsigned int* status;    // device word the kernels OR error bits into (bit 0: a bounded wait on the tensor
+                             // core ran out in the tcgen05 multi-row kernel); may be null
     float scale;             // score scale, 1/sqrt(D) by default
     SeqDesc seq[kMaxSeqsPerLaunch];
 };
@@ -156,6 +158,13 @@ bool decode_f16_supported(uint32_t head_dim, uint32_t rows);
 // Multi-row causal attention over an f16 cache (chunked prefill / speculative verify).
 cudaError_t launch_verify_f16(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);
 bool verify_f16_supported(uint32_t head_dim, uint32_t rows, uint32_t group);
+// The same contract on the tcgen05 tensor cores (head_dim 128): accumulators in tensor memory, one CTA per SM.
+// A cell of its scratch is a (sequence, head chunk, block of verify_tc_pairs_per_cta row-head pairs).
+cudaError_t launch_verify_tc(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);
+bool verify_tc_supported(uint32_t head_dim, uint32_t rows, uint32_t group);
+uint32_t verify_tc_pairs_per_cta(uint32_t rows, uint32_t group);
+uint32_t verify_tc_pair_chunks(uint32_t rows, uint32_t group);
+cudaError_t configure_verify_tc();
 // General kernel: any head_dim <= 256, any rows, f32 or f16 cache (CUDA cores, f32 math).
 cudaError_t launch_attn_general(const AttnLaunch& p, bool f16, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_snapshot_copy(const CopyLaunch& p, cudaStream_t s, uint64_t* launches);
