@@ -166,7 +166,9 @@ def run_spec_verify(args, sampler_cls):
                    "mean_context": sum(pos) / SESSIONS, "l2": f"{bytes_launch / 2**20:.0f} MiB of K/V per launch, larger than L2"},
         "roofline": {"bound": "hbm", "achieved": bytes_launch / (a_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": bytes_launch / (a_ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src,
-                     "kernel": "verify_f16_kernel<128>", "bytes_per_launch": bytes_launch, "avg_launch_ms": a_ms,
+                     "kernel": ("verify_tc_kernel<32> (tcgen05)" if os.environ.get("ITK_VERIFY_TC", "1") != "0"
+                                else "verify_f16_kernel<128> (mma.sync)"),
+                     "bytes_per_launch": bytes_launch, "avg_launch_ms": a_ms,
                      "launches_timed": prof["attention_launches"],
                      "append_avg_launch_ms": prof["append_ms"] / max(prof["append_launches"], 1),
                      "tensor_tflops": flops_launch / (a_ms * 1e-3) / 1e12, "kv_splits": be.stats()["last_splits"]},

@@ -1,37 +1,59 @@
 // Multi-row causal GQA attention over the f16 resident cache on the 5th-generation tensor cores
-// (tcgen05.mma, accumulators in tensor memory): the speculative verify block and chunked-prefill rows.
+// (tcgen05.mma, operands and accumulators in tensor memory): the speculative verify block and
+// chunked-prefill rows.
 //
 // Same contract as the mma.sync kernel next door (attn_verify_f16.cu): gqa_attention with several queries
 // (crates/attention/src/attention.rs:160-213) after the block's rows were appended
 // (crates/arch-llama/src/model.rs:212-228); row r sits at position q_pos0 + r and sees keys kp <= its
 // position (kp > position - window on a sliding layer).
 //
-// One CTA (128 threads = the 128 lanes of tensor memory) owns a (sequence, KV head, block of row-head
-// pairs, key split).  Per 64-key tile:
-//   S = [q_hi | q_lo] * [K | K]^T   16 MMAs of M128 N64 K16.  The f32 query is carried as two f16 terms
-//                                   laid side by side along the contraction dimension, so one accumulator
-//                                   row receives q_hi.k + q_lo.k = the f32-grade score; the K tile is
-//                                   simply addressed twice.
-//   softmax                         thread i reads row i of S from tensor memory (tcgen05.ld), applies
-//                                   scale and the causal / window mask, keeps a running maximum and sum,
-//                                   and writes the weights as f16 hi and lo terms to a swizzled
-//                                   shared-memory tile P = [p_hi | p_lo].
-//   O += P * [V ; V]                8 MMAs of M128 N128 K16 accumulating in tensor memory; V is consumed
-//                                   in place as an MN-major operand (no transpose in shared memory).
-// The accumulator is rescaled in tensor memory only when a row's maximum grows by more than 2^8 (the
-// stale maximum is used consistently for weights and sum until then, so the result is exact).
+// One CTA owns a (sequence, KV head, block of row-head pairs, key split).  Only the K/V stream lives in shared
+// memory; everything else sits in the 512 columns of tensor memory:
+//
+//   columns   0-127  Q      row i: an f32 query as two f16 terms, [q_hi | q_lo], two halfs per column
+//   columns 128-255  S      scores of a 128-key tile (f32)
+//   columns 256-383  P0,P1  softmax weights of a tile as f16 (two keys per column), double buffered
+//   columns 384-511  O      the output accumulator (f32)
+//
+// Per 128-key tile:
+//   S = [q_hi | q_lo] * [K | K]^T   16 MMAs of M128 N128 K16, A from tensor memory, B = the K tile in shared
+//                                   memory addressed twice: one accumulator row receives q_hi.k + q_lo.k,
+//                                   the f32-grade score.
+//   softmax                         thread i reads row i of S (tcgen05.ld), applies scale and the causal /
+//                                   window mask, keeps a running maximum and sum, and stores the weights as
+//                                   f16 hi and lo terms into P (tcgen05.st).
+//   O += P * V                      8 MMAs of M128 N128 K16, A from tensor memory, B = the V tile consumed in
+//                                   place as an MN-major operand (no transpose in shared memory).  The hi and
+//                                   lo f16 terms of the weights sit in different ROWS (see below), so their
+//                                   products are added once, at the end, instead of doubling the MMAs.
+// One thread can issue a tcgen05.mma about every 64 clocks whatever its N up to 128 (measured), which is
+// also what an N = 128 MMA takes to execute; hence 128-key tiles: the same 32 issues cover twice the keys of
+// a 64-key tile.  S is a single buffer: the softmax threads copy their scores to registers at once and release
+// it, so the next tile's scores are computed underneath the softmax.
+// The accumulator is rescaled in tensor memory only when a row's maximum grows by more than 2^8 (the stale
+// maximum is used consistently for weights and sum until then, so the result is exact).
+//
+// The CTA is warp-specialised (7 warps):
+//   warps 0-3  softmax: thread i owns tensor-memory lane i;
+//   warp  4    issues every MMA (one lane) - issuing blocks while the tensor queue is full, so it must not
+//              sit in a warp that also has softmax work - and owns the tensor-memory allocation;
+//   warp 5 streams K tiles, warp 6 V tiles, with 16-byte cp.async (zero-filled past the split's range)
+//              into rings of three (K) and four (V) 32 KiB stages - a K stage is free again as soon as its
+//              scores are complete, a V stage only after P * V; each copy batch reports its own completion to
+//              the stage's barrier.
+// They meet only through mbarriers: full/empty per stage, scores complete, scores consumed, weights stored, and
+// one that counts completed P * V products.  Every wait is clock-bounded; a wait that runs out raises
+// AttnLaunch::status and every role leaves its loop instead of spinning forever.
 //
 // A verify block has few pairs (7 rows x 4 heads = 28 in the speculative configuration) while the MMA has
-// 128 rows, so the pairs are replicated R = 4, 2 or 1 times over the lane quadrants and replica r takes
-// columns [r*64/R, (r+1)*64/R) of every tile: the R replicas are R interleaved key subsets with their own
-// running maxima, merged at the end like key splits.  The tensor-core cost is the same, the per-thread
-// softmax work drops by R.
+// 128 rows.  A CTA takes PC = 32 or 64 pairs and gives each R = 128 / PC rows: row (r, pair) with r = 2 * kh + x
+// handles key columns [kh * 128 / KH, (kh + 1) * 128 / KH) of every tile (KH = R / 2 interleaved key subsets
+// with their own running maxima) and stores the hi (x = 0) or lo (x = 1) f16 term of its weights; the other
+// columns of its P row stay zero.  All R rows of a pair hold the same query, so their scores are identical;
+// their R partial outputs are merged at the end like key splits.
 //
-// K/V tiles arrive by cp.async (16-byte, zero-filled past the split's range) in a 4-deep ring; all waits on
-// the tensor core go through one mbarrier with a clock-bounded wait that raises AttnLaunch::status instead
-// of spinning forever.
-//
-// Bound: HBM (the block's K/V stream, read once per pair block).
+// Bound: HBM (the block's K/V stream, read once per pair block): a tile's 24 MMAs take about 1550 clocks
+// against about 2500-2900 clocks of HBM time per 64 KiB tile and SM.
 #include "attn_common.cuh"
 #include "tcgen05.cuh"
 
@@ -39,19 +61,21 @@ namespace itk {
 
 namespace {
 
-constexpr int kTcThreads = 128;
-constexpr int kTcTile = 64;   // keys per tile
-constexpr int kTcStages = 4;  // K/V ring depth
-constexpr int kTcD = 128;     // head dimension this kernel is built for
-constexpr uint32_t kPanelQ = 128 * 128;  // bytes of a [128 rows][64 halfs] panel
-constexpr uint32_t kPanelKV = 64 * 128;  // bytes of a [64 keys][64 halfs] panel
-constexpr uint32_t kQBytes = 4 * kPanelQ;       // q_hi d0-63, q_hi d64-127, q_lo d0-63, q_lo d64-127
-constexpr uint32_t kPBytes = 2 * kPanelQ;       // p_hi, p_lo over the tile's 64 keys
-constexpr uint32_t kStageBytes = 4 * kPanelKV;  // K (2 panels) then V (2 panels)
-constexpr uint32_t kTcSmemUsed = kQBytes + kPBytes + kTcStages * kStageBytes + 64;
+constexpr int kTcSoftmaxThreads = 128;
+constexpr int kTcLoaderThreads = 32;  // per stream (K, V)
+constexpr int kTcThreads = kTcSoftmaxThreads + 32 + 2 * kTcLoaderThreads;
+constexpr int kTcMmaWarp = 4;
+constexpr int kTcTile = 128;   // keys per tile
+constexpr int kTcStagesK = 3;  // K ring depth
+constexpr int kTcStagesV = 4;  // V ring depth
+constexpr int kTcD = 128;      // head dimension this kernel is built for
+constexpr uint32_t kPanelKV = kTcTile * 128;    // bytes of a [128 keys][64 halfs] panel
+constexpr uint32_t kStageBytes = 2 * kPanelKV;  // a K (or V) tile: channels 0-63, then 64-127
+constexpr uint32_t kTcBarBytes = 256;
+constexpr uint32_t kTcSmemUsed = (kTcStagesK + kTcStagesV) * kStageBytes + kTcBarBytes;
 constexpr uint32_t kTcSmemBytes = kTcSmemUsed + 1024;  // slack to align the base to 1024 bytes
-constexpr uint32_t kTmemCols = 256;                    // S in columns 0-63, O in columns 128-255
-constexpr uint32_t kTmemO = 128;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemQ = 0, kTmemS = 128, kTmemP = 256, kTmemO = 384;
 constexpr long long kWaitClocks = 2000000000ll;  // about a second
 constexpr float kRescaleStep = 8.f;              // log2 of the growth of a row maximum that triggers a rescale
 constexpr int kStageRowFloats = kTcD + 4;        // epilogue staging row (padded against bank conflicts)
@@ -60,23 +84,58 @@ __device__ __forceinline__ uint32_t panel_off(uint32_t row, uint32_t chunk) {
     return row * 128 + ((chunk ^ (row & 7)) << 4);
 }
 
-// CN = columns of a 64-key tile each thread handles = 64 / replicas; pairs per CTA = 2 * CN.
-template <int CN>
+
+// Barrier among the 128 softmax threads only (hardware barrier 1; barrier 0 is __syncthreads of the whole CTA).
+__device__ __forceinline__ void softmax_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar_addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_addr) : "memory");
+}
+
+// The mbarrier gets one arrival (counted against its initial count) once every cp.async this thread issued before
+// has written its bytes.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar_addr) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+// Bounded wait; a wait that runs out raises the CTA's abort flag, which every role polls once per tile.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag) {
+    if (tc::mbar_wait_bounded(bar_addr, parity, kWaitClocks)) return true;
+    *abort_flag = 1;
+    return false;
+}
+
+// PC = pairs per CTA (32 or 64).
+template <int PC>
 __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_constant__ AttnLaunch p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    constexpr int R = kTcTile / CN;
-    constexpr int PC = kTcThreads / R;
+    constexpr int R = kTcSoftmaxThreads / PC;  // rows per pair
+    constexpr int KH = R / 2;                  // key subsets
+    constexpr int CN = kTcTile / KH;           // tile columns a softmax thread handles
     constexpr int D = kTcD;
 
     unsigned char* smem =
         reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    const uint32_t sbase = smem_u32(smem);
-    const uint32_t qbuf = sbase, pbuf = sbase + kQBytes, kvbuf = pbuf + kPBytes;
-    const uint32_t bar = kvbuf + kTcStages * kStageBytes, slot = bar + 8;
-    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (slot - sbase));
-    int* s_flag = reinterpret_cast<int*>(smem + (slot - sbase) + 4);
+    const uint32_t kbuf = smem_u32(smem), vbuf = kbuf + kTcStagesK * kStageBytes;
+    // mbarriers (8 bytes each) behind the rings
+    const uint32_t bars = vbuf + kTcStagesV * kStageBytes;
+    const uint32_t bar_full_k = bars;                     // [stage] the K tile's bytes are in shared memory
+    const uint32_t bar_empty_k = bar_full_k + 8 * kTcStagesK;  // [stage] the scores reading it are complete
+    const uint32_t bar_full_v = bar_empty_k + 8 * kTcStagesK;
+    const uint32_t bar_empty_v = bar_full_v + 8 * kTcStagesV;  // [stage] the P * V reading it is complete
+    const uint32_t bar_s = bar_empty_v + 8 * kTcStagesV;  // the tile's scores are complete
+    const uint32_t bar_sfree = bar_s + 8;                 // every softmax thread holds its scores in registers
+    const uint32_t bar_p = bar_s + 16;                    // [2] the weights of even / odd tiles are stored
+    const uint32_t bar_o = bar_s + 32;                    // one phase per completed P * V
+    const uint32_t bar_q = bar_o + 8;                     // Q and the zeroed P buffers are in tensor memory
+    const uint32_t bar_go = bar_q + 8;                    // the query rows have arrived (and left their staging area)
+    const uint32_t slot = bar_go + 8;
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (slot - kbuf));
+    int* s_flag = reinterpret_cast<int*>(smem + (slot - kbuf) + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (slot - kbuf) + 8);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t split = blockIdx.x, seq = blockIdx.z;
     const uint32_t gheads = min(p.group, static_cast<uint32_t>(kHeadsPerCta));
     const uint32_t pchunks = (p.rows * gheads + PC - 1) / PC;
@@ -96,224 +155,311 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t k1 = min(n, k0 + chunk);
     const uint32_t span = k1 - k0;
     const uint32_t ntiles = (span + kTcTile - 1) / kTcTile;
-    const uint32_t s0 = (sd.kv_lo + k0) % ring;
-    const size_t stream = (static_cast<size_t>(sd.slot) * p.layer.kv_heads + kvh) * ring * D;
-    const __half* kbase = static_cast<const __half*>(p.layer.k) + stream;
-    const __half* vbase = static_cast<const __half*>(p.layer.v) + stream;
-
-    // Thread tid = tensor-memory lane tid = replica `rep` of pair `lp`; it handles tile columns [col0, col0 + CN).
-    const uint32_t lp = tid % PC, rep = tid / PC, col0 = rep * CN;
-    const uint32_t pair = pc * PC + lp;
-    const bool live = pair < n_pairs;
-    const uint32_t prow = live ? pair / nh : 0, phead = live ? pair % nh : 0;
-    const uint32_t ppos = sd.q_pos0 + prow;
-    uint32_t abs_lo = sd.kv_lo;
-    if (window != 0 && ppos + 1 > window) abs_lo = max(abs_lo, ppos + 1 - window);
-    const int64_t rel0 = static_cast<int64_t>(sd.kv_lo) + k0;
-    const int64_t vis_lo = live ? static_cast<int64_t>(abs_lo) - rel0 : 0;
-    const int64_t vis_hi = live ? static_cast<int64_t>(ppos) + 1 - rel0 : 0;
-
-    auto load_tile = [&](uint32_t tile) {
-        const uint32_t kst = kvbuf + (tile % kTcStages) * kStageBytes, vst = kst + 2 * kPanelKV;
-        const uint32_t row0 = tile * kTcTile;
-#pragma unroll
-        for (int i = 0; i < kTcTile * (D / 8) / kTcThreads; ++i) {
-            const int cid = i * kTcThreads + tid;
-            const uint32_t row = cid / (D / 8), c = cid % (D / 8);
-            const uint32_t kr = row0 + row;
-            const bool valid = kr < span;
-            uint32_t srow = s0 + kr;
-            if (srow >= ring) srow -= ring;
-            const size_t goff = static_cast<size_t>(valid ? srow : 0u) * D + c * 8;
-            const uint32_t soff = (c / 8) * kPanelKV + panel_off(row, c % 8);
-            cp_async16(kst + soff, kbase + goff, valid ? 16u : 0u);
-            cp_async16(vst + soff, vbase + goff, valid ? 16u : 0u);
-        }
-    };
-
-    // The K/V stream starts first; everything else is set up underneath it.
-#pragma unroll
-    for (int s = 0; s < kTcStages - 1; ++s) {
-        if (static_cast<uint32_t>(s) < ntiles) load_tile(s);
-        cp_async_commit();
-    }
 
     if (tid == 0) {
-        tc::mbar_init(bar, 1);
+        for (int s = 0; s < kTcStagesK; ++s) {
+            tc::mbar_init(bar_full_k + 8 * s, kTcLoaderThreads);
+            tc::mbar_init(bar_empty_k + 8 * s, 1);
+        }
+        for (int s = 0; s < kTcStagesV; ++s) {
+            tc::mbar_init(bar_full_v + 8 * s, kTcLoaderThreads);
+            tc::mbar_init(bar_empty_v + 8 * s, 1);
+        }
+        tc::mbar_init(bar_s, 1);
+        tc::mbar_init(bar_sfree, kTcSoftmaxThreads);
+        tc::mbar_init(bar_p, kTcSoftmaxThreads);
+        tc::mbar_init(bar_p + 8, kTcSoftmaxThreads);
+        tc::mbar_init(bar_o, 1);
+        tc::mbar_init(bar_q, kTcSoftmaxThreads);
+        tc::mbar_init(bar_go, kTcSoftmaxThreads);
+        *abort_flag = 0;
         tc::fence_mbar_init();
     }
-    __syncwarp();
-    if (warp == 0) {
+    if (warp == kTcMmaWarp) {
         tc::tmem_alloc(slot, kTmemCols);
         tc::tmem_relinquish();
     }
-    {   // Row tid of the query tile: hi and lo f16 terms of the pair's f32 query; row tid of P starts as zeros.
-        const float* qrow = p.q + ((static_cast<size_t>(seq) * p.rows + prow) * p.q_heads + head0 + phead) * D;
-#pragma unroll 4
-        for (int c = 0; c < D / 8; ++c) {
-            float x[8];
-            if (live) {
-                const float4 a = *reinterpret_cast<const float4*>(qrow + 8 * c);
-                const float4 b = *reinterpret_cast<const float4*>(qrow + 8 * c + 4);
-                x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
-                x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = 0.f;
-            }
-            uint32_t hi[4], lo[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                __half h0, l0, h1, l1;
-                split_half(x[2 * e], h0, l0);
-                split_half(x[2 * e + 1], h1, l1);
-                hi[e] = pack_half2(h0, h1);
-                lo[e] = pack_half2(l0, l1);
-            }
-            const uint32_t off = (c / 8) * kPanelQ + panel_off(tid, c % 8);
-            *reinterpret_cast<uint4*>(smem + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(smem + 2 * kPanelQ + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            *reinterpret_cast<uint4*>(smem + kQBytes + panel_off(tid, c)) = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(smem + kQBytes + kPanelQ + panel_off(tid, c)) = make_uint4(0u, 0u, 0u, 0u);
-        }
-    }
-
-
-    cp_async_wait<kTcStages - 2>();  // tile 0 has landed (tiles 1 and 2 may still be in flight)
-    tc::fence_proxy_async();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = *slot_ptr;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tS = tmem + lane_base + col0;
-    const uint32_t tO = tmem + lane_base + kTmemO;
 
-    constexpr uint32_t kIdescS = tc::instr_desc_f16(128, kTcTile, false);
-    constexpr uint32_t kIdescO = tc::instr_desc_f16(128, D, true);
-    auto issue_qk = [&](uint32_t tile) {  // S = [q_hi | q_lo] * [K | K]^T, 16 halfs of the contraction per MMA
-        const uint32_t kst = kvbuf + (tile % kTcStages) * kStageBytes;
-#pragma unroll
-        for (int ks = 0; ks < 16; ++ks)
-            tc::mma_f16_ss(tmem, tc::smem_desc(qbuf + (ks / 4) * kPanelQ + (ks % 4) * 32, 16, 1024),
-                           tc::smem_desc(kst + ((ks % 8) / 4) * kPanelKV + (ks % 4) * 32, 16, 1024), kIdescS,
-                           ks > 0 ? 1u : 0u);
-    };
-    auto issue_pv = [&](uint32_t tile) {  // O (+)= [p_hi | p_lo] * [V ; V], 16 keys per MMA
-        const uint32_t vst = kvbuf + (tile % kTcStages) * kStageBytes + 2 * kPanelKV;
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            tc::mma_f16_ss(tmem + kTmemO, tc::smem_desc(pbuf + (j / 4) * kPanelQ + (j % 4) * 32, 16, 1024),
-                           tc::smem_desc(vst + (j % 4) * 2048, kPanelKV, 1024), kIdescO,
-                           (tile > 0 || j > 0) ? 1u : 0u);
-    };
-    if (tid == 0 && ntiles > 0) {
-        issue_qk(0);
-        tc::mma_commit(bar);
-    }
-    __syncwarp();
-
-    float m_use = -INFINITY, l = 0.f;  // the maximum the weights are taken against (log2 domain), their sum
-    const float sl = p.scale * kLog2e;
-    uint32_t phase = 0;
-    bool failed = false;
-    for (uint32_t tile = 0; tile < ntiles; ++tile) {
-        // S of this tile is complete, and so is every MMA issued before it: the stage of tile - 1 is free.
-        const bool ok = tc::mbar_wait_bounded(bar, phase, kWaitClocks);
-        phase ^= 1u;
-        tc::fence_after_sync();
-        if (tile + kTcStages - 1 < ntiles) load_tile(tile + kTcStages - 1);
-        cp_async_commit();
-
-        uint32_t sr[CN / 16][16];
-#pragma unroll
-        for (int b = 0; b < CN / 16; ++b) tc::tmem_ld16(tS + 16 * b, sr[b]);
-        tc::tmem_wait_ld();
-        const int64_t kr0 = static_cast<int64_t>(tile) * kTcTile + col0;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int b = 0; b < CN / 16; ++b)
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int64_t kr = kr0 + 16 * b + j;
-                float v = __uint_as_float(sr[b][j]) * sl;
-                v = (kr >= vis_lo && kr < vis_hi) ? v : -INFINITY;
-                sr[b][j] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
+    if (warp > kTcMmaWarp) {
+        // ---------------- loaders: warp 5 streams K, warp 6 streams V; thread lt copies 16-byte chunk c of rows
+        // rg, rg + 2, ... of every tile
+        const bool is_v = warp > kTcMmaWarp + 1;
+        const uint32_t lt = (tid - (kTcMmaWarp + 1) * 32) % kTcLoaderThreads;
+        const uint32_t c = lt % (D / 8), rg = lt / (D / 8);
+        const uint32_t s0 = (sd.kv_lo + k0) % ring;
+        const size_t stream = (static_cast<size_t>(sd.slot) * p.layer.kv_heads + kvh) * ring * D + c * 8;
+        const __half* col = static_cast<const __half*>(is_v ? p.layer.v : p.layer.k) + stream;
+        const uint32_t soff_c = (c / 8) * kPanelKV, cc = c % 8;
+        const uint32_t nst = is_v ? kTcStagesV : kTcStagesK;
+        const uint32_t buf = is_v ? vbuf : kbuf;
+        const uint32_t bar_full = is_v ? bar_full_v : bar_full_k, bar_empty = is_v ? bar_empty_v : bar_empty_k;
+        for (uint32_t tile = 0; tile < ntiles; ++tile) {
+            if (*abort_flag != 0) break;
+            const uint32_t st = tile % nst;
+            // Only the first K tile is requested before the query rows have arrived: a load issued together with
+            // the CTAs' opening burst of hundreds of KiB each waits microseconds for its turn, and the first scores
+            // need the queries.  (The last V stage also doubles as the staging area of the query rows.)
+            if (tile == (is_v ? 0u : 1u) && !wait_or_abort(bar_go, 0u, abort_flag)) break;
+            if (tile >= nst && !wait_or_abort(bar_empty + 8 * st, (tile / nst - 1) & 1u, abort_flag)) break;
+            const uint32_t dst = buf + st * kStageBytes;
+            const uint32_t row0 = tile * kTcTile;
+#pragma unroll 8
+            for (int i = 0; i < kTcTile / 2; ++i) {
+                const uint32_t row = rg + 2 * i;
+                const uint32_t kr = row0 + row;
+                const bool valid = kr < span;
+                uint32_t srow = s0 + kr;
+                if (srow >= ring) srow -= ring;
+                cp_async16(dst + soff_c + panel_off(row, cc), col + static_cast<size_t>(valid ? srow : 0u) * D,
+                           valid ? 16u : 0u);
             }
-        const bool grow = mx > m_use + kRescaleStep;  // also the first visible key of the row (m_use = -inf)
-        const float m_new = grow ? mx : m_use;
-        const float corr = grow ? (m_use == -INFINITY ? 0.f : fast_exp2(m_use - m_new)) : 1.f;
-        if (tile > 0 && __ballot_sync(0xffffffffu, grow) != 0u) {
-            // Some row of this warp moves its maximum: rescale the warp's 32 accumulator rows in tensor memory
-            // (every MMA into them has completed, see the wait above).
-#pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 16) {
-                uint32_t r[16];
-                tc::tmem_ld16(tO + c0, r);
-                tc::tmem_wait_ld();
+            // The stage's full barrier receives this thread's arrival when the copies above have landed; nobody waits.
+            cp_async_arrive_noinc(bar_full + 8 * st);
+        }
+        cp_async_wait_all();
+    } else if (warp == kTcMmaWarp) {
+        // ---------------- MMA issuer: one lane issues everything (tcgen05.commit tracks that thread's MMAs)
+        if (lane == 0 && ntiles > 0) {
+            constexpr uint32_t kIdescS = tc::instr_desc_f16(128, kTcTile, false);
+            constexpr uint32_t kIdescO = tc::instr_desc_f16(128, D, true);
+            auto issue_qk = [&](uint32_t tile) {  // S = [q_hi | q_lo] * [K | K]^T, 16 halfs of the contraction per MMA
+                const uint32_t kst = kbuf + (tile % kTcStagesK) * kStageBytes;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
-                tc::tmem_st16(tO + c0, r);
+                for (int ks = 0; ks < 16; ++ks)
+                    tc::mma_f16_ts(tmem + kTmemS, tmem + kTmemQ + 8 * ks,
+                                   tc::smem_desc(kst + ((ks % 8) / 4) * kPanelKV + (ks % 4) * 32, 16, 1024), kIdescS,
+                                   ks > 0 ? 1u : 0u);
+                tc::mma_commit(bar_empty_k + 8 * (tile % kTcStagesK));  // the K tile has been consumed
+                tc::mma_commit(bar_s);
+            };
+            auto issue_pv = [&](uint32_t tile) {  // O (+)= P * V, 16 keys per MMA
+                const uint32_t vst = vbuf + (tile % kTcStagesV) * kStageBytes;
+                const uint32_t a = tmem + kTmemP + (tile & 1u) * (kTcTile / 2);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    tc::mma_f16_ts(tmem + kTmemO, a + 8 * j, tc::smem_desc(vst + j * 2048, kPanelKV, 1024), kIdescO,
+                                   (tile > 0 || j > 0) ? 1u : 0u);
+                tc::mma_commit(bar_empty_v + 8 * (tile % kTcStagesV));  // the V tile has been consumed
+                tc::mma_commit(bar_o);
+            };
+            if (wait_or_abort(bar_q, 0u, abort_flag) && wait_or_abort(bar_full_k, 0u, abort_flag)) {
+                tc::fence_proxy_async();  // the tile was written through the generic proxy (cp.async)
+                tc::fence_after_sync();
+                issue_qk(0);
+                for (uint32_t tile = 0; tile < ntiles; ++tile) {
+                    if (*abort_flag != 0) break;
+                    if (tile + 1 < ntiles) {
+                        // The next tile's scores run underneath this tile's softmax, as soon as every softmax
+                        // thread has taken this tile's scores into registers.
+                        if (!wait_or_abort(bar_full_k + 8 * ((tile + 1) % kTcStagesK), ((tile + 1) / kTcStagesK) & 1u,
+                                           abort_flag))
+                            break;
+                        if (!wait_or_abort(bar_sfree, tile & 1u, abort_flag)) break;
+                        tc::fence_proxy_async();
+                        tc::fence_after_sync();
+                        issue_qk(tile + 1);
+                    }
+                    if (!wait_or_abort(bar_p + 8 * (tile & 1u), (tile >> 1) & 1u, abort_flag)) break;
+                    if (!wait_or_abort(bar_full_v + 8 * (tile % kTcStagesV), (tile / kTcStagesV) & 1u, abort_flag)) break;
+                    tc::fence_proxy_async();
+                    tc::fence_after_sync();
+                    issue_pv(tile);
+                }
             }
-            tc::tmem_wait_st();
-        }
-        l *= corr;
-        m_use = m_new;
-        const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-#pragma unroll
-        for (int jc = 0; jc < CN / 8; ++jc) {
-            uint32_t hi[4], lo[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float p0 = fast_exp2(__uint_as_float(sr[jc / 2][(jc % 2) * 8 + 2 * e]) - m_safe);
-                const float p1 = fast_exp2(__uint_as_float(sr[jc / 2][(jc % 2) * 8 + 2 * e + 1]) - m_safe);
-                l += p0 + p1;
-                __half h0, l0, h1, l1;
-                split_half(p0, h0, l0);
-                split_half(p1, h1, l1);
-                hi[e] = pack_half2(h0, h1);
-                lo[e] = pack_half2(l0, l1);
-            }
-            const uint32_t off = panel_off(tid, col0 / 8 + jc);
-            *reinterpret_cast<uint4*>(smem + kQBytes + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(smem + kQBytes + kPanelQ + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-        cp_async_wait<kTcStages - 2>();  // the next tile has landed
-        tc::fence_proxy_async();
-        tc::fence_before_sync();
-        if (__syncthreads_or(ok ? 0 : 1)) {  // a wait ran out somewhere: every thread leaves together
-            failed = true;
-            break;
-        }
-        if (tid == 0) {
-            tc::fence_after_sync();
-            issue_pv(tile);
-            if (tile + 1 < ntiles) issue_qk(tile + 1);  // S was read into registers by everyone before the barrier
-            tc::mma_commit(bar);
         }
         __syncwarp();
-    }
-    if (!failed && ntiles > 0) {
-        const bool ok = tc::mbar_wait_bounded(bar, phase, kWaitClocks);  // the last P * V
-        if (__syncthreads_or(ok ? 0 : 1)) failed = true;
-    }
-    cp_async_wait<0>();
-    tc::fence_after_sync();
-    __syncthreads();  // nothing is in flight into shared memory any more: the K/V ring becomes staging space
-
-    if (failed) {
-        if (tid == 0 && p.status) atomicOr(p.status, 1u);
     } else {
-        float* stage_o = reinterpret_cast<float*>(smem + kQBytes + kPBytes);  // [128][D + 4]
-        float* stage_ml = stage_o + kTcThreads * kStageRowFloats;             // [128][2]
+        // ---------------- softmax: thread tid = tensor-memory lane tid = row r = 2 * kh + x of pair lp: it handles
+        // tile columns [col0, col0 + CN) in blocks of 64 and stores the hi (x = 0) or lo (x = 1) term of the weights.
+        constexpr int SB = 64;
+        constexpr int NSB = CN / SB;
+        const uint32_t lp = tid % PC, r = tid / PC, x = r & 1u, col0 = (r >> 1) * CN;
+        const uint32_t pair = pc * PC + lp;
+        const bool live = pair < n_pairs;
+        const uint32_t prow = live ? pair / nh : 0, phead = live ? pair % nh : 0;
+        const uint32_t ppos = sd.q_pos0 + prow;
+        uint32_t abs_lo = sd.kv_lo;
+        if (window != 0 && ppos + 1 > window) abs_lo = max(abs_lo, ppos + 1 - window);
+        // Visible keys of the row, as indices into this CTA's slice: [vis_lo, vis_hi).  Rows without a pair see
+        // everything (their results are never stored), so they do not force the masked path below.
+        constexpr int64_t kFar = 1ll << 30;
+        const int64_t rel0 = static_cast<int64_t>(sd.kv_lo) + k0;
+        const int32_t vis_lo =
+            live ? static_cast<int32_t>(max(-kFar, min(kFar, static_cast<int64_t>(abs_lo) - rel0))) : -static_cast<int32_t>(kFar);
+        const int32_t vis_hi =
+            live ? static_cast<int32_t>(max(-kFar, min(kFar, static_cast<int64_t>(ppos) + 1 - rel0))) : static_cast<int32_t>(kFar);
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t tO = tmem + lane_base + kTmemO;
+        const uint32_t tS = tmem + lane_base + kTmemS + col0;
+
+        {   // Row tid of Q: hi terms of the 128 channels in columns 0-63, lo terms in columns 64-127.
+            // Coalesced first: a warp instruction loads one whole 512-byte row (lane l takes 16-byte chunk l), each
+            // warp a quarter of the CTA's PC distinct rows, into a staging area in shared memory (chunk l of row i
+            // at position l ^ (i & 31): conflict-free both ways).  Then every thread reads the row of its pair.
+            unsigned char* stage_q = smem + (vbuf - kbuf) + (kTcStagesV - 1) * kStageBytes;
+            {
+                float4 ld[PC / 4];
+#pragma unroll
+                for (int rr = 0; rr < PC / 4; ++rr) {
+                    const uint32_t srow = warp * (PC / 4) + rr, spair = pc * PC + srow;
+                    ld[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (spair < n_pairs)
+                        ld[rr] = __ldg(reinterpret_cast<const float4*>(
+                                           p.q + ((static_cast<size_t>(seq) * p.rows + spair / nh) * p.q_heads + head0 +
+                                                  spair % nh) * D) + lane);
+                }
+#pragma unroll
+                for (int rr = 0; rr < PC / 4; ++rr) {
+                    const uint32_t srow = warp * (PC / 4) + rr;
+                    *reinterpret_cast<float4*>(stage_q + srow * 512 + ((lane ^ (srow & 31u)) << 4)) = ld[rr];
+                }
+            }
+            softmax_sync();
+            // (a rolled loop: one-time code is kept small)
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {  // 32 channels = 16 columns of hi and 16 of lo
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 v4 = *reinterpret_cast<const float4*>(
+                        stage_q + lp * 512 + ((static_cast<uint32_t>(8 * c + j) ^ (lp & 31u)) << 4));
+                    __half h0, l0, h1, l1;
+                    split_half(v4.x, h0, l0);
+                    split_half(v4.y, h1, l1);
+                    hi[2 * j] = pack_half2(h0, h1);
+                    lo[2 * j] = pack_half2(l0, l1);
+                    split_half(v4.z, h0, l0);
+                    split_half(v4.w, h1, l1);
+                    hi[2 * j + 1] = pack_half2(h0, h1);
+                    lo[2 * j + 1] = pack_half2(l0, l1);
+                }
+                tc::tmem_st16(tmem + lane_base + kTmemQ + 16 * c, hi);
+                tc::tmem_st16(tmem + lane_base + kTmemQ + 64 + 16 * c, lo);
+            }
+            mbar_arrive(bar_go);  // (release) the staging area may be overwritten by the V stream
+            // Both P buffers start as zeros: a row only ever writes its own columns.
+            uint32_t z[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) z[j] = 0u;
+#pragma unroll 1
+            for (int c = 0; c < kTcTile; c += 16) tc::tmem_st16(tmem + lane_base + kTmemP + c, z);
+            tc::tmem_wait_st();
+            tc::fence_before_sync();
+            mbar_arrive(bar_q);
+        }
+
+        float m_use = -INFINITY, l = 0.f;  // the maximum the weights are taken against (log2 domain), their sum
+        const float sl = p.scale * kLog2e;
+        bool done = ntiles > 0;  // every product into O has completed (nothing to wait for when there is no tile)
+        for (uint32_t tile = 0; tile < ntiles; ++tile) {
+            if (__any_sync(0xffffffffu, *abort_flag != 0)) { done = false; break; }
+            // The scores of this tile are complete, and so is every MMA issued before them (up to P * V of
+            // tile - 2, which read the P buffer this tile writes).
+            if (!__all_sync(0xffffffffu, wait_or_abort(bar_s, tile & 1u, abort_flag))) { done = false; break; }
+            tc::fence_after_sync();
+            const int32_t kr0 = static_cast<int32_t>(tile * kTcTile + col0);
+            // Tiles wholly inside every row's visible range (all but the causal edge and a window's trailing edge)
+            // skip the masks.
+            const bool masked = __any_sync(0xffffffffu, kr0 < vis_lo || kr0 + CN > vis_hi);
+            uint32_t sr[SB / 16][16];
+            // Raw scores of block sb into sr (masked ones become -inf); returns their maximum.
+            auto load_block = [&](int sb) {
+#pragma unroll
+                for (int i = 0; i < SB / 16; ++i) tc::tmem_ld16(tS + sb * SB + 16 * i, sr[i]);
+                tc::tmem_wait_ld();
+                float mx = -INFINITY;
+                if (masked) {
+#pragma unroll
+                    for (int i = 0; i < SB / 16; ++i)
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int32_t kr = kr0 + sb * SB + 16 * i + j;
+                            if (kr < vis_lo || kr >= vis_hi) sr[i][j] = 0xff800000u;  // -inf
+                        }
+                }
+#pragma unroll
+                for (int i = 0; i < SB / 16; ++i)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) mx = fmaxf(mx, __uint_as_float(sr[i][j]));
+                return mx;
+            };
+            float mx = load_block(0);
+            if constexpr (NSB == 2) mx = fmaxf(mx, load_block(1));
+            mx *= sl;  // sl > 0: the maximum of the scaled scores
+            if constexpr (NSB == 1) {
+                tc::fence_before_sync();
+                mbar_arrive(bar_sfree);  // the scores are in registers: the next tile's may overwrite them
+            }
+            const bool grow = mx > m_use + kRescaleStep;  // also the first visible key of the row (m_use = -inf)
+            const float m_new = grow ? mx : m_use;
+            const float corr = grow ? (m_use == -INFINITY ? 0.f : fast_exp2(m_use - m_new)) : 1.f;
+            if (tile > 0 && __ballot_sync(0xffffffffu, grow) != 0u) {
+                // Some row of this warp moves its maximum: once the previous tile's P * V has completed, rescale
+                // the warp's 32 accumulator rows in tensor memory.
+                if (!__all_sync(0xffffffffu, wait_or_abort(bar_o, (tile - 1) & 1u, abort_flag))) { done = false; break; }
+                tc::fence_after_sync();
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 16) {
+                    uint32_t o16[16];
+                    tc::tmem_ld16(tO + c0, o16);
+                    tc::tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o16[j] = __float_as_uint(__uint_as_float(o16[j]) * corr);
+                    tc::tmem_st16(tO + c0, o16);
+                }
+            }
+            l *= corr;
+            m_use = m_new;
+            const float neg_m = (m_use == -INFINITY) ? 0.f : -m_use;
+            const uint32_t tP = tmem + lane_base + kTmemP + (tile & 1u) * (kTcTile / 2) + col0 / 2;
+#pragma unroll
+            for (int sb = 0; sb < NSB; ++sb) {
+                if constexpr (NSB == 2) {
+                    load_block(sb);
+                    if (sb == NSB - 1) {
+                        tc::fence_before_sync();
+                        mbar_arrive(bar_sfree);
+                    }
+                }
+                // weights = 2^(score * scale - max); this row keeps their f16 hi or lo term, two keys per column
+#pragma unroll
+                for (int i = 0; i < SB / 16; ++i) {
+                    uint32_t w8[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i][2 * e]), sl, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i][2 * e + 1]), sl, neg_m));
+                        l += p0 + p1;
+                        __half2 h2 = __floats2half2_rn(p0, p1);
+                        if (x != 0u) {
+                            const float2 hf = __half22float2(h2);
+                            h2 = __floats2half2_rn(p0 - hf.x, p1 - hf.y);
+                        }
+                        w8[e] = *reinterpret_cast<const uint32_t*>(&h2);
+                    }
+                    tc::tmem_st8(tP + (sb * SB) / 2 + 8 * i, w8);
+                }
+            }
+            tc::tmem_wait_st();
+            tc::fence_before_sync();
+            mbar_arrive(bar_p + 8 * (tile & 1u));  // weights stored
+        }
+        if (done) done = __all_sync(0xffffffffu, wait_or_abort(bar_o, (ntiles - 1) & 1u, abort_flag));  // the last P * V
+        tc::fence_after_sync();
+        const bool have_o = done;
+        if (x != 0u) l = 0.f;  // the hi and lo rows of a pair saw the same weights: their sum counts once
+        softmax_sync();  // the rings are idle now (every tile was consumed): they become staging space
+
+        float* stage_o = reinterpret_cast<float*>(smem);                  // [128][D + 4]
+        float* stage_ml = stage_o + kTcSoftmaxThreads * kStageRowFloats;  // [128][2]
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 16) {
             uint32_t r[16];
-            if (ntiles > 0) {
+            if (have_o) {
                 tc::tmem_ld16(tO + c0, r);
                 tc::tmem_wait_ld();
             } else {
@@ -329,33 +475,34 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         stage_ml[2 * tid] = m_use;
         stage_ml[2 * tid + 1] = l;
         tc::fence_before_sync();
-        __syncthreads();
+        softmax_sync();
 
-        // Merge the R replicas of pair lp; this thread produces channels [rep * DW, (rep + 1) * DW).
+        // Merge the R rows of pair lp; this thread produces channels [rep * DW, (rep + 1) * DW).
+        const uint32_t rep = r;
         constexpr int DW = D / R;
         float M = -INFINITY, L = 0.f;
         float w[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) M = fmaxf(M, stage_ml[2 * (r * PC + lp)]);
+        for (int rr = 0; rr < R; ++rr) M = fmaxf(M, stage_ml[2 * (rr * PC + lp)]);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float ms = stage_ml[2 * (r * PC + lp)];
-            w[r] = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
-            L += w[r] * stage_ml[2 * (r * PC + lp) + 1];
+        for (int rr = 0; rr < R; ++rr) {
+            const float ms = stage_ml[2 * (rr * PC + lp)];
+            w[rr] = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+            L += w[rr] * stage_ml[2 * (rr * PC + lp) + 1];
         }
         float4 acc[DW / 4];
 #pragma unroll
         for (int i = 0; i < DW / 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float4* src = reinterpret_cast<const float4*>(stage_o + (r * PC + lp) * kStageRowFloats + rep * DW);
+        for (int rr = 0; rr < R; ++rr) {
+            const float4* src = reinterpret_cast<const float4*>(stage_o + (rr * PC + lp) * kStageRowFloats + rep * DW);
 #pragma unroll
             for (int i = 0; i < DW / 4; ++i) {
                 const float4 v = src[i];
-                acc[i].x += w[r] * v.x;
-                acc[i].y += w[r] * v.y;
-                acc[i].z += w[r] * v.z;
-                acc[i].w += w[r] * v.w;
+                acc[i].x += w[rr] * v.x;
+                acc[i].y += w[rr] * v.y;
+                acc[i].z += w[rr] * v.z;
+                acc[i].w += w[rr] * v.w;
             }
         }
 
@@ -383,18 +530,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                 }
             }
             __threadfence();
-            __syncthreads();
+            softmax_sync();
             if (tid == 0) {
                 const unsigned int ticket = atomicAdd(p.tickets + cell, 1u);
                 *s_flag = (ticket == p.splits - 1) ? 1 : 0;
             }
-            __syncthreads();
+            softmax_sync();
             if (*s_flag != 0) {  // the last CTA of the cell merges every split
                 __threadfence();
                 const float* all_o = p.part_o + cell * p.splits * PC * D;
                 const float* all_ml = p.part_ml + cell * p.splits * PC * 2;
                 const uint32_t cta_pairs = min(static_cast<uint32_t>(PC), n_pairs - pc * PC);
-                for (uint32_t idx = tid; idx < cta_pairs * (D / 4); idx += kTcThreads) {
+                for (uint32_t idx = tid; idx < cta_pairs * (D / 4); idx += kTcSoftmaxThreads) {
                     const uint32_t q = idx / (D / 4), d4 = idx % (D / 4);
                     float Mx = -INFINITY;
                     for (uint32_t s = 0; s < p.splits; ++s)
@@ -414,9 +561,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                         o.w += ws * v.w;
                     }
                     const uint32_t gp = pc * PC + q;
-                    const uint32_t r = gp / nh, h = gp % nh;
+                    const uint32_t orow = gp / nh, h = gp % nh;
                     const float inv = 1.f / Ls;
-                    reinterpret_cast<float4*>(p.out + ((static_cast<size_t>(seq) * p.rows + r) * p.q_heads + head0 + h) *
+                    reinterpret_cast<float4*>(p.out + ((static_cast<size_t>(seq) * p.rows + orow) * p.q_heads + head0 + h) *
                                                           D)[d4] = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
                 }
                 if (tid == 0) p.tickets[cell] = 0u;
@@ -425,12 +572,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     }
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 0) tc::tmem_dealloc(tmem, kTmemCols);
+    if (tid == 0 && *abort_flag != 0 && p.status) atomicOr(p.status, 1u);
+    if (warp == kTcMmaWarp) tc::tmem_dealloc(tmem, kTmemCols);
 }
 
-uint32_t tc_columns_for(uint32_t rows, uint32_t group) {
+uint32_t tc_pairs_for(uint32_t rows, uint32_t group) {
     const uint32_t pairs = rows * (group < static_cast<uint32_t>(kHeadsPerCta) ? group : kHeadsPerCta);
-    return pairs <= 32 ? 16u : pairs <= 64 ? 32u : 64u;
+    return pairs <= 32 ? 32u : 64u;
 }
 
 }  // namespace
@@ -440,7 +588,7 @@ bool verify_tc_supported(uint32_t head_dim, uint32_t rows, uint32_t group) {
     return rows >= 2 && rows <= 64 && head_dim == static_cast<uint32_t>(kTcD);
 }
 
-uint32_t verify_tc_pairs_per_cta(uint32_t rows, uint32_t group) { return 2 * tc_columns_for(rows, group); }
+uint32_t verify_tc_pairs_per_cta(uint32_t rows, uint32_t group) { return tc_pairs_for(rows, group); }
 
 uint32_t verify_tc_pair_chunks(uint32_t rows, uint32_t group) {
     const uint32_t nh = group < static_cast<uint32_t>(kHeadsPerCta) ? group : kHeadsPerCta;
@@ -449,11 +597,8 @@ uint32_t verify_tc_pair_chunks(uint32_t rows, uint32_t group) {
 }
 
 cudaError_t configure_verify_tc() {
-    cudaError_t e = cudaFuncSetAttribute(verify_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(verify_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(kTcSmemBytes));
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(verify_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(kTcSmemBytes));
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(verify_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kTcSmemBytes));
@@ -464,11 +609,10 @@ cudaError_t launch_verify_tc(const AttnLaunch& p, cudaStream_t s, uint64_t* laun
     if (p.layer.head_dim != static_cast<uint32_t>(kTcD)) return cudaErrorInvalidValue;
     const uint32_t pchunks = verify_tc_pair_chunks(p.rows, p.group);
     const dim3 grid(p.splits, p.layer.kv_heads * p.gchunks * pchunks, p.n_seqs);
-    switch (tc_columns_for(p.rows, p.group)) {
-        case 16: verify_tc_kernel<16><<<grid, kTcThreads, kTcSmemBytes, s>>>(p); break;
-        case 32: verify_tc_kernel<32><<<grid, kTcThreads, kTcSmemBytes, s>>>(p); break;
-        default: verify_tc_kernel<64><<<grid, kTcThreads, kTcSmemBytes, s>>>(p); break;
-    }
+    if (tc_pairs_for(p.rows, p.group) == 32)
+        verify_tc_kernel<32><<<grid, kTcThreads, kTcSmemBytes, s>>>(p);
+    else
+        verify_tc_kernel<64><<<grid, kTcThreads, kTcSmemBytes, s>>>(p);
     if (launches) *launches += 1;
     return cudaGetLastError();
 }
