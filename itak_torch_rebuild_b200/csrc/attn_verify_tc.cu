@@ -41,6 +41,9 @@
 //              into rings of three (K) and four (V) 32 KiB stages - a K stage is free again as soon as its
 //              scores are complete, a V stage only after P * V; each copy batch reports its own completion to
 //              the stage's barrier.
+// With AttnLaunch::k_new set the loaders also do the block's append: tiles that hold the block's own rows take
+// them from the caller's f32 rows (converted with the append kernel's function) instead of the cache, and one CTA
+// per (sequence, KV head) stores them to the cache, which saves the separate append launch.
 // They meet only through mbarriers: full/empty per stage, scores complete, scores consumed, weights stored, and
 // one that counts completed P * V products.  Every wait is clock-bounded; a wait that runs out raises
 // AttnLaunch::status and every role leaves its loop instead of spinning forever.
@@ -55,6 +58,7 @@
 // Bound: HBM (the block's K/V stream, read once per pair block): a tile's 24 MMAs take about 1550 clocks
 // against about 2500-2900 clocks of HBM time per 64 KiB tile and SM.
 #include "attn_common.cuh"
+#include "kv_convert.cuh"
 #include "tcgen05.cuh"
 
 namespace itk {
@@ -127,8 +131,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t bar_s = bar_empty_v + 8 * kTcStagesV;  // the tile's scores are complete
     const uint32_t bar_sfree = bar_s + 8;                 // every softmax thread holds its scores in registers
     const uint32_t bar_p = bar_s + 16;                    // [2] the weights of even / odd tiles are stored
-    const uint32_t bar_o = bar_s + 32;                    // one phase per completed P * V
-    const uint32_t bar_q = bar_o + 8;                     // Q and the zeroed P buffers are in tensor memory
+    const uint32_t bar_o = bar_s + 32;                    // [2] P * V of even / odd tiles has completed
+    const uint32_t bar_q = bar_o + 16;                    // Q and the zeroed P buffers are in tensor memory
     const uint32_t bar_go = bar_q + 8;                    // the query rows have arrived (and left their staging area)
     const uint32_t slot = bar_go + 8;
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem + (slot - kbuf));
@@ -170,6 +174,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         tc::mbar_init(bar_p, kTcSoftmaxThreads);
         tc::mbar_init(bar_p + 8, kTcSoftmaxThreads);
         tc::mbar_init(bar_o, 1);
+        tc::mbar_init(bar_o + 8, 1);
         tc::mbar_init(bar_q, kTcSoftmaxThreads);
         tc::mbar_init(bar_go, kTcSoftmaxThreads);
         *abort_flag = 0;
@@ -197,6 +202,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         const uint32_t nst = is_v ? kTcStagesV : kTcStagesK;
         const uint32_t buf = is_v ? vbuf : kbuf;
         const uint32_t bar_full = is_v ? bar_full_v : bar_full_k, bar_empty = is_v ? bar_empty_v : bar_empty_k;
+        // Fused append (AttnLaunch::k_new): the block's own rows [q_pos0, q_pos0 + rows) come from the caller's f32
+        // rows [n_seqs][rows][kv_heads][D]; new_rel = index of q_pos0 inside this CTA's slice.
+        const float* new_base = is_v ? p.v_new : p.k_new;
+        const float* new_src =
+            new_base ? new_base + (static_cast<size_t>(seq) * p.rows * p.layer.kv_heads + kvh) * D + c * 8 : nullptr;
+        const int64_t new_rel = static_cast<int64_t>(sd.q_pos0) - (static_cast<int64_t>(sd.kv_lo) + k0);
+        const bool stores_new = gc == 0 && pc == 0;
         for (uint32_t tile = 0; tile < ntiles; ++tile) {
             if (*abort_flag != 0) break;
             const uint32_t st = tile % nst;
@@ -207,6 +219,33 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             if (tile >= nst && !wait_or_abort(bar_empty + 8 * st, (tile / nst - 1) & 1u, abort_flag)) break;
             const uint32_t dst = buf + st * kStageBytes;
             const uint32_t row0 = tile * kTcTile;
+            if (new_src != nullptr && static_cast<int64_t>(row0) + kTcTile > new_rel) {
+                // The tile holds rows of the block itself, which no append launch has stored: they are converted
+                // here from the caller's f32 rows (the append kernel's conversion), dropped straight into the stage,
+                // and stored to the cache by the one CTA of this (sequence, KV head) that is in charge of that.
+                for (int i = 0; i < kTcTile / 2; ++i) {
+                    const uint32_t row = rg + 2 * i;
+                    const uint32_t kr = row0 + row;
+                    const bool valid = kr < span;
+                    uint32_t srow = s0 + kr;
+                    if (srow >= ring) srow -= ring;
+                    if (valid && static_cast<int64_t>(kr) >= new_rel) {
+                        const float* src = new_src + static_cast<size_t>(kr - new_rel) * p.layer.kv_heads * D;
+                        const uint4 packed = pack8(*reinterpret_cast<const float4*>(src),
+                                                   *reinterpret_cast<const float4*>(src + 4));
+                        *reinterpret_cast<uint4*>(smem + (dst - kbuf) + soff_c + panel_off(row, cc)) = packed;
+                        if (stores_new)
+                            *reinterpret_cast<uint4*>(const_cast<__half*>(col) + static_cast<size_t>(srow) * D) = packed;
+                    } else {
+                        cp_async16(dst + soff_c + panel_off(row, cc), col + static_cast<size_t>(valid ? srow : 0u) * D,
+                                   valid ? 16u : 0u);
+                    }
+                }
+                cp_async_wait_all();
+                tc::fence_proxy_async();  // plain stores into the stage: visible to the tensor core before the arrival
+                mbar_arrive(bar_full + 8 * st);
+                continue;
+            }
 #pragma unroll 8
             for (int i = 0; i < kTcTile / 2; ++i) {
                 const uint32_t row = rg + 2 * i;
@@ -244,7 +283,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                     tc::mma_f16_ts(tmem + kTmemO, a + 8 * j, tc::smem_desc(vst + j * 2048, kPanelKV, 1024), kIdescO,
                                    (tile > 0 || j > 0) ? 1u : 0u);
                 tc::mma_commit(bar_empty_v + 8 * (tile % kTcStagesV));  // the V tile has been consumed
-                tc::mma_commit(bar_o);
+                tc::mma_commit(bar_o + 8 * (tile & 1u));
             };
             if (wait_or_abort(bar_q, 0u, abort_flag) && wait_or_abort(bar_full_k, 0u, abort_flag)) {
                 tc::fence_proxy_async();  // the tile was written through the generic proxy (cp.async)
@@ -400,7 +439,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             if (tile > 0 && __ballot_sync(0xffffffffu, grow) != 0u) {
                 // Some row of this warp moves its maximum: once the previous tile's P * V has completed, rescale
                 // the warp's 32 accumulator rows in tensor memory.
-                if (!__all_sync(0xffffffffu, wait_or_abort(bar_o, (tile - 1) & 1u, abort_flag))) { done = false; break; }
+                // (A parity wait is only unambiguous while the waiter is at most one phase behind: hence one barrier
+                // for even and one for odd tiles - the product of tile - 3 is known complete, that of tile + 1 cannot
+                // have been issued.)
+                if (!__all_sync(0xffffffffu, wait_or_abort(bar_o + 8 * ((tile - 1) & 1u), ((tile - 1) >> 1) & 1u, abort_flag))) {
+                    done = false;
+                    break;
+                }
                 tc::fence_after_sync();
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 16) {
@@ -448,7 +493,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             tc::fence_before_sync();
             mbar_arrive(bar_p + 8 * (tile & 1u));  // weights stored
         }
-        if (done) done = __all_sync(0xffffffffu, wait_or_abort(bar_o, (ntiles - 1) & 1u, abort_flag));  // the last P * V
+        // The last two products: the scores of the last tile only vouch for those up to tile ntiles - 3.
+        if (done && ntiles > 1)
+            done = __all_sync(0xffffffffu, wait_or_abort(bar_o + 8 * ((ntiles - 2) & 1u), ((ntiles - 2) >> 1) & 1u, abort_flag));
+        if (done)
+            done = __all_sync(0xffffffffu, wait_or_abort(bar_o + 8 * ((ntiles - 1) & 1u), ((ntiles - 1) >> 1) & 1u, abort_flag));
         tc::fence_after_sync();
         const bool have_o = done;
         if (x != 0u) l = 0.f;  // the hi and lo rows of a pair saw the same weights: their sum counts once

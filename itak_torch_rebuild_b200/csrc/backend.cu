@@ -253,8 +253,8 @@ int check_status(itk_backend* b) {
 }
 
 // Launch attention for `n` sequences of `rows` rows each (device q / out).
-// `d_k_new` / `d_v_new` (device f32 [n][kv_heads*D], may be null): the step's new rows for the decode kernel to
-// store itself; only honoured when the decode kernel takes the launch (see decode_fuses_append).
+// `d_k_new` / `d_v_new` (device f32 [n][rows][kv_heads*D], may be null): the launch's new rows for the decode or
+// the tcgen05 multi-row kernel to store itself (see decode_fuses_append, verify_fuses_append).
 int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, uint32_t rows, const float* d_q,
                   float* d_out, const float* d_k_new = nullptr, const float* d_v_new = nullptr) {
     const uint32_t D = b->cfg.head_dim;
@@ -324,6 +324,10 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
             // one CTA per SM; a partial slot holds verify_tc_pairs_per_cta rows instead of 8
             p.splits = choose_splits(b, cells, n_max, 64, itk::verify_tc_pairs_per_cta(rows, b->group) / 8, 1);
             b->stats.last_splits = p.splits;
+            if (d_k_new) {
+                p.k_new = d_k_new + static_cast<size_t>(at) * rows * b->row_len();
+                p.v_new = d_v_new + static_cast<size_t>(at) * rows * b->row_len();
+            }
             b->status_pending = true;
             ITK_CUDA(b, itk::launch_verify_tc(p, b->stream, &b->stats.kernel_launches), "tensor-core attention launch");
             prof_end(b, ev);
@@ -345,6 +349,12 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
 // row itself; ITK_SEPARATE_APPEND=1 keeps the two-launch form for A/B checks.
 bool decode_fuses_append(const itk_backend* b, uint32_t rows) {
     return b->f16 && !b->separate_append && (b->cfg.head_dim % 8 == 0) && itk::decode_f16_supported(b->cfg.head_dim, rows);
+}
+
+// So does the tcgen05 multi-row kernel (its loader warps convert and store the block's rows).
+bool verify_fuses_append(const itk_backend* b, uint32_t rows) {
+    return b->f16 && !b->separate_append && !b->force_general && b->verify_tc && rows > 1 &&
+           itk::verify_tc_supported(b->cfg.head_dim, rows, b->group);
 }
 
 // Shared validation of one attention step; fills `seqs`.  Mirrors
@@ -403,7 +413,7 @@ int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t*
                 uint32_t rows, const float* d_q, const float* d_k, const float* d_v, float* d_out) {
     std::vector<SeqDesc> seqs;
     if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
-    const bool fuse = decode_fuses_append(b, rows);
+    const bool fuse = decode_fuses_append(b, rows) || verify_fuses_append(b, rows);
     if (!fuse)
         if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
     for (uint32_t i = 0; i < n_seqs; ++i) {

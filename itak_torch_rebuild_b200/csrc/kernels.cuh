@@ -85,8 +85,9 @@ struct AttnLaunch {
     uint32_t splits;         // partial slots per cell in the scratch: the CTAs along a key range (general and
                              // verify kernels) or the most CTAs that can share one cell (decode kernel)
     uint32_t tiles_per_cta;  // decode kernel: 64-key tiles each persistent CTA walks
-    const float* k_new;      // decode kernel: when set, the step's new K rows [n_seqs][kv_heads][D] (f32); the
-    const float* v_new;      // kernel stores them at position kv_hi - 1 itself instead of a separate append
+    const float* k_new;      // decode and tcgen05 multi-row kernels: when set, the launch's new K rows
+    const float* v_new;      // [n_seqs][rows][kv_heads][D] (f32); the kernel stores them at positions q_pos0.. itself
+                             // instead of a separate append launch
     uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
