@@ -97,10 +97,10 @@ constexpr int kMaxSplits = 256;  // upper bound on the partials merged for one c
 // Otherwise the partial goes to global scratch (p.splits slots per cell), the
 // CTA takes a ticket, and the CTA that draws the last ticket merges every part
 // (log-sum-exp) and writes the output; nobody waits.
-// The merge is two passes so that its global loads are independent of each
-// other: first the (max, sum) pairs of every split become per-split weights in
-// `wscratch` (shared memory, 2 * MAXP * 8 + 8 floats), then every output channel
-// is a weighted sum over splits with several loads in flight.
+// The merge's global loads are independent of each other: the (max, sum) pairs
+// of every split (which become per-split weights in `wscratch`, shared memory,
+// 2 * MAXP * 8 + 8 floats) and the first batch of partial outputs are requested
+// together; every output channel is then a weighted sum over splits.
 // The ticket counter is left at zero for the next launch.
 template <int THREADS, int MAXP>
 __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t n_parts,
@@ -127,75 +127,110 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
     }
     __threadfence();
     __syncthreads();
+    ITK_TRACE(p, 8);
     if (tid == 0) {
         const unsigned int ticket = atomicAdd(p.tickets + cell, 1u);
         *s_flag = (ticket == n_parts - 1) ? 1 : 0;
     }
     __syncthreads();
+    ITK_TRACE(p, 9);
     if (*s_flag == 0) return;
+    ITK_TRACE(p, 6);  // this CTA drew the last ticket of a cell and merges it
     __threadfence();
     const float* all_o = p.part_o + cell * p.splits * (kHeadsPerCta * D);
     const float* all_ml = p.part_ml + cell * p.splits * (kHeadsPerCta * 2);
     float* w_m = wscratch;                        // [splits][8] maxima, then weights
     float* w_l = wscratch + MAXP * kHeadsPerCta;  // [parts][8] sums
     float* inv_l = w_l + MAXP * kHeadsPerCta;     // [8]
-    for (uint32_t i = tid; i < n_parts * kHeadsPerCta; i += THREADS) {
-        const uint32_t h = i % kHeadsPerCta;
-        float ms = -INFINITY, ls = 0.f;
-        if (h < nh) {
-            ms = __ldcg(all_ml + 2 * i);
-            ls = __ldcg(all_ml + 2 * i + 1);
-        }
-        w_m[i] = ms;
-        w_l[i] = ls;
-    }
-    __syncthreads();
-    if (tid < nh) {
-        float M = -INFINITY;
-        for (uint32_t s = 0; s < n_parts; ++s) M = fmaxf(M, w_m[s * kHeadsPerCta + tid]);
-        float L = 0.f;
-        for (uint32_t s = 0; s < n_parts; ++s) {
-            const float ms = w_m[s * kHeadsPerCta + tid];
-            const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
-            w_m[s * kHeadsPerCta + tid] = w;
-            L += w * w_l[s * kHeadsPerCta + tid];
-        }
-        inv_l[tid] = 1.f / L;
-    }
-    __syncthreads();
-    if ((D & 3u) == 0) {
-        // Vector path: a thread owns up to two float4 columns and keeps 8 parts x 2 columns of loads in flight,
-        // so merging a cell that dozens of CTAs shared costs a few memory round trips, not dozens.
-        const uint32_t cols = nh * D / 4;
-        const size_t pstride = kHeadsPerCta * D / 4;  // float4s per part
-        const float4* src4 = reinterpret_cast<const float4*>(all_o);
-        for (uint32_t c0 = tid; c0 < cols; c0 += 2 * THREADS) {
-            const uint32_t c1 = c0 + THREADS;
-            const bool two = c1 < cols;
-            const uint32_t h0 = (c0 * 4) / D, h1 = two ? (c1 * 4) / D : h0;
-            float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-            for (uint32_t s = 0; s < n_parts; s += 8) {
-                float4 v0[8], v1[8];
+    // Vector path: a thread owns up to two float4 columns and keeps kBatch parts x 2 columns of loads in flight.
+    // The partial outputs do not depend on the weights, so the first batch is requested together with the
+    // (max, sum) pairs: merging a cell that dozens of CTAs shared costs two or three memory round trips.
+    constexpr int kBatch = 13;
+    const bool vec = (D & 3u) == 0;
+    const uint32_t cols = nh * D / 4;
+    const size_t pstride = kHeadsPerCta * D / 4;  // float4s per part
+    const float4* src4 = reinterpret_cast<const float4*>(all_o);
+    uint32_t c0 = tid, c1 = tid + THREADS;
+    bool one = vec && c0 < cols, two = vec && c1 < cols;
+    float4 v0[kBatch], v1[kBatch];
+    auto load_batch = [&](uint32_t s) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t si = s + i < n_parts ? s + i : s;  // clamped; its weight is zeroed below
-                    v0[i] = __ldcg(src4 + si * pstride + c0);
-                    v1[i] = two ? __ldcg(src4 + si * pstride + c1) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+        for (int i = 0; i < kBatch; ++i) {
+            const uint32_t si = s + i < n_parts ? s + i : s;  // clamped; its weight is zeroed below
+            v0[i] = one ? __ldcg(src4 + si * pstride + c0) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v1[i] = two ? __ldcg(src4 + si * pstride + c1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    if (vec) load_batch(0);
+    {   // the (max, sum) pairs of every part, requested together (a fixed trip count keeps the loads independent)
+        constexpr int kRounds = (MAXP * kHeadsPerCta + THREADS - 1) / THREADS;
+        float2 ml[kRounds];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const bool ok = s + i < n_parts;
-                    const float w0 = ok ? w_m[(s + i) * kHeadsPerCta + h0] : 0.f;
-                    const float w1 = ok ? w_m[(s + i) * kHeadsPerCta + h1] : 0.f;
-                    a0.x += w0 * v0[i].x; a0.y += w0 * v0[i].y; a0.z += w0 * v0[i].z; a0.w += w0 * v0[i].w;
-                    a1.x += w1 * v1[i].x; a1.y += w1 * v1[i].y; a1.z += w1 * v1[i].z; a1.w += w1 * v1[i].w;
-                }
+        for (int r = 0; r < kRounds; ++r) {
+            const uint32_t i = tid + r * THREADS;
+            ml[r] = make_float2(-INFINITY, 0.f);
+            if (i < n_parts * kHeadsPerCta && i % kHeadsPerCta < nh)
+                ml[r] = __ldcg(reinterpret_cast<const float2*>(all_ml) + i);
+        }
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) {
+            const uint32_t i = tid + r * THREADS;
+            if (i < n_parts * kHeadsPerCta) {
+                w_m[i] = ml[r].x;
+                w_l[i] = ml[r].y;
             }
-            const float i0 = inv_l[h0], i1 = inv_l[h1];
-            store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
-            if (two) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
         }
-    } else {
+    }
+    __syncthreads();
+    ITK_TRACE(p, 10);
+    if (tid < 32) {  // the whole first warp (the shuffles name every lane): four lanes per head, 8 heads
+        const uint32_t h = tid >> 2, q = tid & 3u;
+        const bool live = h < nh;
+        float M = -INFINITY;
+        if (live)
+            for (uint32_t s = q; s < n_parts; s += 4) M = fmaxf(M, w_m[s * kHeadsPerCta + h]);
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 1));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 2));
+        float L = 0.f;
+        if (live)
+            for (uint32_t s = q; s < n_parts; s += 4) {
+                const float ms = w_m[s * kHeadsPerCta + h];
+                const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+                w_m[s * kHeadsPerCta + h] = w;
+                L += w * w_l[s * kHeadsPerCta + h];
+            }
+        L += __shfl_xor_sync(0xffffffffu, L, 1);
+        L += __shfl_xor_sync(0xffffffffu, L, 2);
+        if (live && q == 0) inv_l[h] = 1.f / L;
+    }
+    __syncthreads();
+    ITK_TRACE(p, 11);
+    for (uint32_t base = 0; vec && base < cols; base += 2 * THREADS) {  // one round unless nh * D > 8 * THREADS
+        if (base != 0) {
+            c0 = base + tid;
+            c1 = c0 + THREADS;
+            one = c0 < cols;
+            two = c1 < cols;
+        }
+        const uint32_t h0 = one ? (c0 * 4) / D : 0u, h1 = two ? (c1 * 4) / D : h0;
+        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+        for (uint32_t s = 0; s < n_parts; s += kBatch) {
+            if (s != 0 || base != 0) load_batch(s);
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const bool ok = s + i < n_parts;
+                const float w0 = ok ? w_m[(s + i) * kHeadsPerCta + h0] : 0.f;
+                const float w1 = ok ? w_m[(s + i) * kHeadsPerCta + h1] : 0.f;
+                a0.x += w0 * v0[i].x; a0.y += w0 * v0[i].y; a0.z += w0 * v0[i].z; a0.w += w0 * v0[i].w;
+                a1.x += w1 * v1[i].x; a1.y += w1 * v1[i].y; a1.z += w1 * v1[i].z; a1.w += w1 * v1[i].w;
+            }
+        }
+        ITK_TRACE(p, 12);
+        const float i0 = inv_l[h0], i1 = inv_l[h1];
+        if (one) store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
+        if (two) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
+    }
+    if (!vec) {
         for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
             const uint32_t h = idx / D;
             const float* src = all_o + idx;

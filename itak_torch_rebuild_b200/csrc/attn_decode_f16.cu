@@ -14,6 +14,11 @@
 // run crosses a cell boundary finishes its part of the first cell and moves
 // on; each part writes an (m, l, o) partial and the last CTA to arrive at a
 // cell merges them (finish_unit).  Nobody waits for anybody.
+// A CTA that crosses a cell boundary pays that cell's epilogue (and a fresh
+// query load and pipeline refill) in the middle of its run and finishes late,
+// so when the cells are alike enough that giving each its own whole number of
+// CTAs lengthens no run by more than a sixteenth, the plan is cell-aligned
+// instead: floor(CTAs * T_cell / total) CTAs per cell, equal runs inside it.
 //
 // Inside a CTA each of the 4 warps owns a private cp.async pipeline over its
 // own 16-key slice of every tile: 16-byte coalesced loads into XOR-swizzled
@@ -46,6 +51,9 @@ namespace {
 constexpr int kDecodeThreads = 128;
 constexpr int kDecodeWarps = 4;
 constexpr int kTileKeys = 64;  // keys per CTA tile = 16 per warp
+// Work plan in shared memory: cum[65] tiles before each sequence, abase[65] first CTA of each sequence in the
+// cell-aligned plan, then per sequence its visible keys, first storage row and slot, then the plan's mode word.
+constexpr int kPlanWords = 2 * (kMaxSeqsPerLaunch + 4) + 3 * kMaxSeqsPerLaunch + 4;
 
 // A walker's place in the launch's tile sequence (warp-uniform).
 struct TileCursor {
@@ -87,7 +95,7 @@ constexpr size_t decode_smem_bytes() {
     // + cumulative tile table
     return decode_pipe_bytes<D, STAGES>() +
            (kDecodeWarps * kHeadsPerCta * 32 + kHeadsPerCta * D + 2 * kDecodeWarps * kHeadsPerCta + 2 * kHeadsPerCta + 4 +
-            2 * kDecodeMaxParts * kHeadsPerCta + kHeadsPerCta + (kMaxSeqsPerLaunch + 4)) * sizeof(float);
+            2 * kDecodeMaxParts * kHeadsPerCta + kHeadsPerCta + kPlanWords) * sizeof(float);
 }
 
 template <int D, int STAGES>
@@ -115,34 +123,60 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
     const bool fused = p.k_new != nullptr;
 
+    ITK_TRACE(p, 0);
     if (p.pdl != 0) pdl_launch_dependents();
     if (p.pdl == 1) pdl_wait();
-    // cum[s] = tiles of all cells before sequence s
+    uint32_t* abase = cum + (kMaxSeqsPerLaunch + 4);
+    uint32_t* sn = abase + (kMaxSeqsPerLaunch + 4);  // visible keys per sequence
+    uint32_t* ss0 = sn + kMaxSeqsPerLaunch;          // storage row of its first visible key
+    uint32_t* sslot = ss0 + kMaxSeqsPerLaunch;
+    uint32_t* mode = sslot + kMaxSeqsPerLaunch;      // [0] 1 = cell-aligned plan
+    if (static_cast<uint32_t>(tid) < p.n_seqs) {     // one global read per sequence, all in flight together
+        const SeqDesc sd = seq_of(p, tid);
+        sn[tid] = sd.kv_hi - sd.kv_lo;
+        ss0[tid] = sd.kv_lo % ring;
+        sslot[tid] = sd.slot;
+    }
+    __syncthreads();
     if (tid == 0) {
+        // cum[s] = tiles of all cells before sequence s
         uint32_t c = 0;
         for (uint32_t s = 0; s < p.n_seqs; ++s) {
             cum[s] = c;
-            const SeqDesc sd = seq_of(p, s);
-            c += (sd.kv_hi - sd.kv_lo + kTileKeys - 1) / kTileKeys * HY;
+            c += (sn[s] + kTileKeys - 1) / kTileKeys * HY;
         }
         cum[p.n_seqs] = c;
+        // The cell-aligned plan, if it costs at most a sixteenth more tiles per CTA than equal runs would.
+        const uint32_t G = gridDim.x, total = c;
+        const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
+        bool ok = total >= G;
+        uint32_t b = 0, worst = 0;
+        for (uint32_t s = 0; s < p.n_seqs && ok; ++s) {
+            const uint32_t T = (sn[s] + kTileKeys - 1) / kTileKeys;
+            const uint32_t ns = static_cast<uint32_t>(static_cast<uint64_t>(T) * G / total);  // CTAs per cell
+            if (ns == 0) {
+                ok = false;
+                break;
+            }
+            const uint32_t run = (T + ns - 1) / ns;
+            if ((T + run - 1) / run > p.splits) ok = false;  // more parts than the scratch has slots per cell
+            worst = max(worst, run);
+            abase[s] = b;
+            b += ns * HY;
+        }
+        abase[p.n_seqs] = b;
+        mode[0] = (ok && worst <= per + max(1u, per / 16u)) ? 1u : 0u;
     }
     __syncthreads();
     const uint32_t total = cum[p.n_seqs];
+    const bool aligned = mode[0] != 0u;
     const uint32_t per = p.seq_dev ? (total + gridDim.x - 1) / gridDim.x : p.tiles_per_cta;
-    const uint32_t g0 = blockIdx.x * per;
-    if (g0 >= total) {
-        if (p.pdl == 2) pdl_wait();
-        return;
-    }
-    const uint32_t ntiles = min(total, g0 + per) - g0;
 
     auto enter_seq = [&](TileCursor& c) {
-        const SeqDesc sd = seq_of(p, c.seq);
-        c.n = sd.kv_hi - sd.kv_lo;
+        c.n = sn[c.seq];
         c.T = (c.n + kTileKeys - 1) / kTileKeys;
-        c.s0 = sd.kv_lo % ring;
-        c.slot = sd.slot;
+        c.s0 = ss0[c.seq];
+        c.slot = sslot[c.seq];
     };
     auto advance = [&](TileCursor& c) {
         if (++c.tile == c.T) {
@@ -154,15 +188,41 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         }
     };
     TileCursor lc;  // load cursor, runs STAGES - 1 tiles ahead of the compute cursor
-    {
-        uint32_t s = 0;
-        while (s + 1 < p.n_seqs && cum[s + 1] <= g0) ++s;
-        lc.seq = s;
-        enter_seq(lc);
-        const uint32_t r = g0 - cum[s];
-        lc.hy = r / lc.T;
-        lc.tile = r % lc.T;
+    uint32_t ntiles = 0;
+    uint32_t al_parts = 0, al_part = 0;  // aligned plan: CTAs sharing this CTA's cell, and which of them this is
+    if (aligned) {
+        if (blockIdx.x < abase[p.n_seqs]) {
+            uint32_t s = 0;
+            while (abase[s + 1] <= blockIdx.x) ++s;
+            lc.seq = s;
+            enter_seq(lc);
+            const uint32_t ns = (abase[s + 1] - abase[s]) / HY;
+            const uint32_t r = blockIdx.x - abase[s];
+            const uint32_t run = (lc.T + ns - 1) / ns;
+            lc.hy = r / ns;
+            al_part = r % ns;
+            al_parts = (lc.T + run - 1) / run;
+            lc.tile = al_part * run;
+            if (lc.tile < lc.T) ntiles = min(run, lc.T - lc.tile);
+        }
+    } else {
+        const uint32_t g0 = blockIdx.x * per;
+        if (g0 < total) {
+            ntiles = min(total, g0 + per) - g0;
+            uint32_t s = 0;
+            while (s + 1 < p.n_seqs && cum[s + 1] <= g0) ++s;
+            lc.seq = s;
+            enter_seq(lc);
+            const uint32_t r = g0 - cum[s];
+            lc.hy = r / lc.T;
+            lc.tile = r % lc.T;
+        }
     }
+    if (ntiles == 0) {
+        if (p.pdl == 2) pdl_wait();
+        return;
+    }
+    ITK_TRACE(p, 1);
     TileCursor cc = lc;
 
     const uint32_t smem_base = smem_u32(smem);
@@ -204,9 +264,31 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         cp_async_commit();
     }
 
+    // While the previous kernel drains (its last CTAs merge the splits and HBM is idle), ask L2 for the next
+    // tiles of this run: one 16-byte-aligned row of K (lanes 0-15) or V (lanes 16-31) per lane.
+    if (p.pdl == 2 && p.l2_prefetch != 0) {
+        TileCursor pc = lc;
+        const uint32_t npf = min(p.l2_prefetch, ntiles - issued);
+        for (uint32_t j = 0; j < npf; ++j) {
+            const uint32_t kvh = pc.hy / p.gchunks;
+            const size_t stream = (static_cast<size_t>(pc.slot) * p.layer.kv_heads + kvh) * ring * D;
+            const uint32_t kr = pc.tile * kTileKeys + warp * 16 + (lane & 15);
+            if (kr < pc.n && !(fused && kr == pc.n - 1)) {
+                uint32_t srow = pc.s0 + kr;
+                if (srow >= ring) srow -= ring;
+                const __half* src = static_cast<const __half*>(lane < 16 ? p.layer.k : p.layer.v) + stream +
+                                    static_cast<size_t>(srow) * D;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(kRowBytes) : "memory");
+            }
+            advance(pc);
+        }
+    }
+
     // The cache rows streamed above do not depend on the previous kernel; the queries, the step's new row
     // and the merge scratch do.
+    ITK_TRACE(p, 2);
     if (p.pdl == 2) pdl_wait();
+    ITK_TRACE(p, 3);
 
     // A layer's inputs exist only once every rank's heads of the previous layer have been gathered: check that the
     // peers' previous launch has arrived here.  The wait is bounded; if it runs out the kernel records that and
@@ -271,6 +353,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         }
         cp_async_wait<STAGES - 2>();
         __syncwarp();
+        if (i == 0) ITK_TRACE(p, 4);
         if (issued < ntiles) {
             load_tile(lc, issued % STAGES);
             advance(lc);
@@ -378,6 +461,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             // a time, then hand the (m, l, o) part to the cell's merge.
             float lq = l + __shfl_xor_sync(0xffffffffu, l, 1);
             lq += __shfl_xor_sync(0xffffffffu, lq, 2);
+            if (i + 1 == ntiles) ITK_TRACE(p, 5);
             __syncthreads();  // the previous cell's epilogue is over for every thread
             if (t == 0) {
                 wm[warp * kHeadsPerCta + g] = m;
@@ -428,15 +512,22 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             }
             __syncthreads();
             // which CTAs share this cell, and which of them this one is
-            const uint32_t gs = cum[cc.seq] + cc.hy * cc.T;
-            const uint32_t first = gs / per, last = (gs + cc.T - 1) / per;
-            finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, last - first + 1, blockIdx.x - first, head0,
-                                                         nh, D, fo, fm, fl, flag, wscratch);
+            if (i + 1 == ntiles) ITK_TRACE(p, 13);
+            uint32_t n_parts = al_parts, part = al_part;
+            if (!aligned) {
+                const uint32_t gs = cum[cc.seq] + cc.hy * cc.T;
+                const uint32_t first = gs / per, last = (gs + cc.T - 1) / per;
+                n_parts = last - first + 1;
+                part = blockIdx.x - first;
+            }
+            finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm, fl, flag,
+                                                         wscratch);
             fresh = true;
         }
         advance(cc);
     }
     cp_async_wait<0>();
+    ITK_TRACE(p, 7);
 }
 
 constexpr int kStages128 = 3;  // 96 KiB of pipeline per CTA at D = 128, two CTAs per SM

@@ -112,6 +112,7 @@ struct itk_backend {
     bool gth_wait = true;  // ITK_GATHER_WAIT=0: do not check the peers' previous launch at kernel start
     int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
     bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
+    uint32_t l2_prefetch = 0; // ITK_DECODE_L2_PREFETCH: tiles per CTA the resident decode kernel requests into L2 before its wait
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append, 2 = snapshot gather / restore scatter
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
@@ -608,6 +609,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
     if (const char* env = std::getenv("ITK_GATHER_WAIT")) b->gth_wait = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
+    if (const char* env = std::getenv("ITK_DECODE_L2_PREFETCH")) b->l2_prefetch = static_cast<uint32_t>(std::atoi(env));
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_VERIFY_TC")) b->verify_tc = std::atoi(env) != 0;
@@ -747,6 +749,21 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
     return ITK_OK;
 }
 
+#ifdef ITK_DECODE_TRACE
+// Timeline build only: [layer][512 CTAs][16] stamps, allocated on request.
+static unsigned long long* g_trace = nullptr;
+extern "C" int itk_debug_trace_buffer(void** dev_ptr, uint64_t* bytes) {
+    const size_t n = 64ull * 512 * 16 * sizeof(unsigned long long);
+    if (!g_trace) {
+        if (cudaMalloc(&g_trace, n) != cudaSuccess) return ITK_ERR_CUDA;
+        cudaMemset(g_trace, 0, n);
+    }
+    *dev_ptr = g_trace;
+    *bytes = n;
+    return ITK_OK;
+}
+#endif
+
 static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
                                float* d_out, bool gather, uint64_t gather_offset_bytes) {
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
@@ -767,6 +784,9 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     p.k_new = d_k;
     p.v_new = d_v;
     p.seq_dev = b->d_states;
+#ifdef ITK_DECODE_TRACE
+    p.trace = g_trace ? g_trace + static_cast<size_t>(layer % 64) * 512 * 16 : nullptr;
+#endif
     if (gather) {
         if (!b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: no gather buffer (itk_gather_create)");
         const uint64_t slot_bytes = static_cast<uint64_t>(p.n_seqs) * b->q_width() * sizeof(float);
@@ -790,6 +810,7 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     }
     // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
     // the same layer) the kernel waits first.
+    p.l2_prefetch = b->l2_prefetch;
     p.pdl = !b->use_pdl ? 0u : ((b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer) ? 2u : 1u);
     ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
              "resident decode launch");

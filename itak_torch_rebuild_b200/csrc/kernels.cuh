@@ -91,14 +91,33 @@ struct AttnLaunch {
     uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
+    uint32_t l2_prefetch;    // decode kernel with pdl == 2: 64-key tiles of its run, beyond those it stages in shared
+                             // memory, that each CTA requests into L2 before it waits for the previous kernel
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
     unsigned int* status;    // device word the kernels OR error bits into (bit 0: a bounded wait on the tensor
                              // core ran out in the tcgen05 multi-row kernel); may be null
     float scale;             // score scale, 1/sqrt(D) by default
+#ifdef ITK_DECODE_TRACE
+    unsigned long long* trace;  // timeline build only: [cta][16] %globaltimer stamps of the decode kernel's phases
+#endif
     SeqDesc seq[kMaxSeqsPerLaunch];
 };
+
+// Timeline stamps of the decode kernel (compiled in only with -DITK_DECODE_TRACE; thread 0 of each CTA).
+#ifdef ITK_DECODE_TRACE
+#define ITK_TRACE(p, i)                                                                     \
+    do {                                                                                    \
+        if ((p).trace && threadIdx.x == 0) {                                                \
+            unsigned long long t_;                                                          \
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t_)::"memory");              \
+            (p).trace[blockIdx.x * 16 + (i)] = t_;                                           \
+        }                                                                                   \
+    } while (0)
+#else
+#define ITK_TRACE(p, i) do { } while (0)
+#endif
 
 struct AppendLaunch {
     void* k;  // layer base of the K slab
