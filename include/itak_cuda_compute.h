@@ -16,7 +16,8 @@
  *  - A backend owns `n_slots` resident sequences ("slots").  Calls on one
  *    backend are serialised by the caller (the reference backend is not Sync).
  *  - Rows arrive already RoPE'd: RoPE is the caller's job, as in
- *    crates/attention/src/attention.rs:5-8.
+ *    crates/attention/src/attention.rs:5-8 - except through the *_prep calls,
+ *    which normalise and rotate raw rows on the device first.
  *  - "host" pointers may be pageable or pinned; "device" pointers must be
  *    device memory on the backend's device, 16-byte aligned.
  *  - There is no CPU fallback: every data-path call launches CUDA kernels and
@@ -168,6 +169,32 @@ int itk_attention_batch_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, 
                                const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
                                const float* d_v, float* d_out);
 
+/* Attention preparation on the device: per-head RMSNorm of the Q and K rows and their rotary rotation, done by
+ * the backend ahead of the append, so that the projections' raw rows never leave the device to be rotated.
+ * Stands in for the reference's fused preparation K9 (crates/wgpu-compute/src/kernels/k9_attn_prep.rs:74-236)
+ * and for the rotation inside the CPU backend's attention step (crates/cpu-compute/src/cpu.rs:598-622, which
+ * rotates on sliding-window layers only).  The arithmetic is the CPU reference's: f64 mean of squares and f64
+ * angles, each result rounded once to f32 (crates/torch-math/src/norm.rs:21-53, rope_interleaved.rs:65-117,
+ * rope.rs:63-117); results agree with it to the last bit or two of f32, not bit for bit.
+ * A NULL weight skips that norm; rotary_dim 0 skips the rotation.  Weights are host pointers, copied. */
+typedef struct itk_prep_config {
+    const float* q_norm_weight; /* [head_dim] or NULL */
+    const float* k_norm_weight; /* [head_dim] or NULL */
+    float norm_eps;             /* finite, > 0 when a weight is given */
+    float rope_base;            /* finite, > 1 when rotary_dim != 0 */
+    uint32_t rotary_dim;        /* 0, or even and <= head_dim */
+    uint32_t pairing;           /* 0 = adjacent pairs (2i, 2i+1) as rope_interleaved; 1 = half split (i, i + rotary_dim/2) as rope */
+} itk_prep_config;
+int itk_layer_prep_set(itk_backend* b, uint32_t layer, const itk_prep_config* cfg);
+/* itk_attention_batch / itk_attention_batch_device taking the projections' raw Q and K rows: prepares them as the
+ * layer's configuration says, then appends and attends as those calls do.  Same shapes, same refusals. */
+int itk_attention_batch_prep(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                             const uint64_t* positions, uint32_t rows, const float* q, const float* k, const float* v,
+                             float* out);
+int itk_attention_batch_prep_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                                    const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
+                                    const float* d_v, float* d_out);
+
 /* A decode loop whose launches depend on no host-side position, so that one step can be recorded once (a
  * CUDA graph) and replayed - the counterpart of the reference session's "one command buffer per forward"
  * (crates/wgpu-compute/src/session.rs:3230-3233).  The listed slots must sit at one position on every layer,
@@ -201,6 +228,23 @@ int itk_gather_reset(itk_backend* b);
 int itk_gather_status(itk_backend* b, uint32_t* error_bits);
 int itk_resident_layer_gather(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
                               uint64_t gather_offset_bytes);
+
+/* Draft-model (DFlash) attention, the attention half of the reference's K17
+ * (crates/wgpu-compute/src/kernels/k17_dflash.rs:109-251; CPU form crates/dflash/src/model.rs:388-466): `rows`
+ * query rows at positions block_start.. attend a position-addressed, possibly sparse set of `committed` rows (row
+ * of position p at p * kv_heads * key_len in d_committed_k, p * kv_heads * value_len in d_committed_v; the list
+ * d_committed_positions says which exist) together with the block's own `block_rows` K/V rows, non-causally unless
+ * `causal`, and within `window` when `sliding` (key kp is hidden from query qp when kp <= qp - window, signed).
+ * All pointers are device f32 / u32; q [rows][q_heads][key_len], out [rows][q_heads][value_len].  No backend handle:
+ * the draft's cache is the caller's (crates/dflash/src/cache.rs:1-24).  key_len and value_len up to 256.  Only queues
+ * work on `cuda_stream`; refusals (the names of k17_dflash.rs:276-316) come back as ITK_ERR_INVALID_ARGUMENT with the
+ * text in error_text. */
+int itk_draft_attention(const float* d_q, const float* d_committed_k, const float* d_committed_v,
+                        const uint32_t* d_committed_positions, uint32_t committed, const float* d_block_k,
+                        const float* d_block_v, uint32_t block_start, uint32_t rows, uint32_t block_rows,
+                        uint32_t q_heads, uint32_t kv_heads, uint32_t key_len, uint32_t value_len, uint32_t causal,
+                        uint32_t sliding, uint32_t window, float scale, float* d_out, void* cuda_stream,
+                        char* error_text, size_t error_text_len);
 
 /* gqa_attention alone (crates/attention/src/attention.rs:104-215) over what a
  * slot already holds: `rows` queries at query_positions[], host buffers.

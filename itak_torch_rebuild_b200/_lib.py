@@ -65,6 +65,17 @@ class Checkpoint(C.Structure):
     ]
 
 
+class PrepConfig(C.Structure):
+    _fields_ = [
+        ("q_norm_weight", C.POINTER(C.c_float)),
+        ("k_norm_weight", C.POINTER(C.c_float)),
+        ("norm_eps", C.c_float),
+        ("rope_base", C.c_float),
+        ("rotary_dim", C.c_uint32),
+        ("pairing", C.c_uint32),
+    ]
+
+
 class Stats(C.Structure):
     _fields_ = [
         ("attention_calls", C.c_uint64),
@@ -92,6 +103,9 @@ SIGNATURES = {
     "itk_attention": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _sz, _u64, _vp]),
     "itk_attention_batch": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_attention_batch_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
+    "itk_layer_prep_set": (C.c_int, [_vp, _u32, C.POINTER(PrepConfig)]),
+    "itk_attention_batch_prep": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
+    "itk_attention_batch_prep_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_resident_begin": (C.c_int, [_vp, _u32, _u32p, _u64]),
     "itk_resident_layer": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "itk_resident_advance": (C.c_int, [_vp]),
@@ -125,6 +139,8 @@ SIGNATURES = {
     "itk_snapshot_from_host_f32": (C.c_int, [_vp, _u64, _u64p, _u64p, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
     "itk_snapshot_to_itkv": (C.c_int, [_vp, _vp, C.c_char_p, _vp, _sz, C.POINTER(_sz)]),
     "itk_snapshot_from_itkv": (C.c_int, [_vp, C.c_char_p, _sz, C.c_char_p, C.POINTER(_vp)]),
+    "itk_draft_attention": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
+                                      _u32, _u32, C.c_float, _vp, _vp, C.c_char_p, _sz]),
     "itk_decode_attention_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _vp, _vp, _u32, _vp,
                                                C.c_char_p, _sz]),
 }

@@ -218,6 +218,53 @@ class CudaCompute:
         self._check(fn(self._h, layer, n, slots_c, positions_c, rows, C.c_void_p(q_ptr), C.c_void_p(k_ptr),
                        C.c_void_p(v_ptr), C.c_void_p(out_ptr)))
 
+    # -- attention preparation on the device (RMSNorm + RoPE ahead of the append) -----------------------------
+    def set_layer_prep(self, layer: int, *, q_norm_weight=None, k_norm_weight=None, norm_eps: float = 1e-6,
+                       rope_base: Optional[float] = None, rotary_dim: Optional[int] = None, pairing: int = 0):
+        """Configure what the ``*_prep`` calls do to a layer's raw Q and K rows: per-head RMSNorm (a ``[head_dim]``
+        weight each, or ``None`` to skip) and the rotation (``rope_base`` ``None`` skips it; ``pairing`` 0 joins
+        channels (2i, 2i+1) as ``rope_interleaved`` does, 1 joins (i, i + rotary_dim/2) as ``rope`` does)."""
+        qw = _host_f32(q_norm_weight).reshape(-1) if q_norm_weight is not None else None
+        kw = _host_f32(k_norm_weight).reshape(-1) if k_norm_weight is not None else None
+        for w in (qw, kw):
+            if w is not None and w.size != self.head_dim:
+                raise CudaComputeError(_lib.ERR_SHAPE_MISMATCH, f"rms_norm: got {w.size}, expected {self.head_dim}")
+        rot = 0 if rope_base is None else (self.head_dim if rotary_dim is None else rotary_dim)
+        cfg = _lib.PrepConfig(C.cast(_ptr(qw), C.POINTER(C.c_float)) if qw is not None else None,
+                              C.cast(_ptr(kw), C.POINTER(C.c_float)) if kw is not None else None,
+                              norm_eps, 0.0 if rope_base is None else rope_base, rot, pairing)
+        self._check(self._lib.itk_layer_prep_set(self._h, layer, C.byref(cfg)))
+
+    def attention_prep(self, layer: int, q, k, v, cache: PositionCache, slot: int = 0) -> np.ndarray:
+        """``attention`` taking the projections' raw rows: the backend normalises and rotates Q and K on the device
+        as ``set_layer_prep`` configured, then appends and attends (crates/cpu-compute/src/cpu.rs:592-646 does the
+        rotation inside its attention step too)."""
+        q, k, v = _host_f32(q).reshape(-1), _host_f32(k).reshape(-1), _host_f32(v).reshape(-1)
+        rows = q.size // self.q_width
+        out = np.empty(max(q.size, 1), dtype=np.float32)
+        sl, ps = (C.c_uint32 * 1)(slot), (C.c_uint64 * 1)(cache.position())
+        self._check(self._lib.itk_attention_batch_prep(self._h, layer, 1, sl, ps, rows, _ptr(q), _ptr(k), _ptr(v),
+                                                       _ptr(out)))
+        return out[: q.size]
+
+    def attention_batch_prep(self, layer: int, slots: Sequence[int], positions: Sequence[int], rows: int, q, k, v
+                             ) -> np.ndarray:
+        n = len(slots)
+        q, k, v = _host_f32(q), _host_f32(k), _host_f32(v)
+        out = np.empty(n * rows * self.q_width, dtype=np.float32)
+        sl = (C.c_uint32 * n)(*slots)
+        ps = (C.c_uint64 * n)(*positions)
+        self._check(self._lib.itk_attention_batch_prep(self._h, layer, n, sl, ps, rows, _ptr(q), _ptr(k), _ptr(v),
+                                                       _ptr(out)))
+        return out
+
+    def attention_batch_prep_ptrs(self, layer: int, slots_c, positions_c, n: int, rows: int, q_ptr: int, k_ptr: int,
+                                  v_ptr: int, out_ptr: int):
+        """Device-pointer form of ``attention_batch_prep``; only queues work."""
+        self._check(self._lib.itk_attention_batch_prep_device(self._h, layer, n, slots_c, positions_c, rows,
+                                                              C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(v_ptr),
+                                                              C.c_void_p(out_ptr)))
+
     # -- replayable decode loop ------------------------------------------------------------------
     def resident_begin(self, slots: Sequence[int], max_steps: int):
         """Reserve ``max_steps`` decode steps for ``slots`` and move their positions to device memory; the step's

@@ -149,23 +149,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         // The cell-aligned plan, if it costs at most a sixteenth more tiles per CTA than equal runs would.
         const uint32_t G = gridDim.x, total = c;
         const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
-        bool ok = total >= G;
-        uint32_t b = 0, worst = 0;
-        for (uint32_t s = 0; s < p.n_seqs && ok; ++s) {
-            const uint32_t T = (sn[s] + kTileKeys - 1) / kTileKeys;
-            const uint32_t ns = static_cast<uint32_t>(static_cast<uint64_t>(T) * G / total);  // CTAs per cell
-            if (ns == 0) {
-                ok = false;
-                break;
-            }
-            const uint32_t run = (T + ns - 1) / ns;
-            if ((T + run - 1) / run > p.splits) ok = false;  // more parts than the scratch has slots per cell
-            worst = max(worst, run);
-            abase[s] = b;
-            b += ns * HY;
-        }
-        abase[p.n_seqs] = b;
-        mode[0] = (ok && worst <= per + max(1u, per / 16u)) ? 1u : 0u;
+        uint32_t worst;
+        mode[0] = decode_aligned_plan(sn, p.n_seqs, HY, G, total, per, p.splits, abase, &worst) ? 1u : 0u;
     }
     __syncthreads();
     const uint32_t total = cum[p.n_seqs];
@@ -254,8 +239,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     };
 
     uint32_t issued = 0;
+    bool waited = p.pdl != 2;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
+        if (!waited && static_cast<uint32_t>(s) >= (p.early_tiles & 0xffu)) {
+            pdl_wait();
+            waited = true;
+        }
         if (issued < ntiles) {
             load_tile(lc, issued % STAGES);
             advance(lc);
@@ -264,30 +254,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         cp_async_commit();
     }
 
-    // While the previous kernel drains (its last CTAs merge the splits and HBM is idle), ask L2 for the next
-    // tiles of this run: one 16-byte-aligned row of K (lanes 0-15) or V (lanes 16-31) per lane.
-    if (p.pdl == 2 && p.l2_prefetch != 0) {
-        TileCursor pc = lc;
-        const uint32_t npf = min(p.l2_prefetch, ntiles - issued);
-        for (uint32_t j = 0; j < npf; ++j) {
-            const uint32_t kvh = pc.hy / p.gchunks;
-            const size_t stream = (static_cast<size_t>(pc.slot) * p.layer.kv_heads + kvh) * ring * D;
-            const uint32_t kr = pc.tile * kTileKeys + warp * 16 + (lane & 15);
-            if (kr < pc.n && !(fused && kr == pc.n - 1)) {
-                uint32_t srow = pc.s0 + kr;
-                if (srow >= ring) srow -= ring;
-                const __half* src = static_cast<const __half*>(lane < 16 ? p.layer.k : p.layer.v) + stream +
-                                    static_cast<size_t>(srow) * D;
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(kRowBytes) : "memory");
-            }
-            advance(pc);
-        }
-    }
-
     // The cache rows streamed above do not depend on the previous kernel; the queries, the step's new row
     // and the merge scratch do.
     ITK_TRACE(p, 2);
-    if (p.pdl == 2) pdl_wait();
+    if (!waited) pdl_wait();
     ITK_TRACE(p, 3);
 
     // A layer's inputs exist only once every rank's heads of the previous layer have been gathered: check that the
@@ -467,18 +437,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 wm[warp * kHeadsPerCta + g] = m;
                 wl[warp * kHeadsPerCta + g] = lq;
             }
+            if (i + 1 == ntiles) {
+                // End of the run: every staged tile has been consumed, so the pipeline's shared memory is free and
+                // the four warps exchange whole rows at once (row stride D + 8 floats: conflict-free both ways).
+                constexpr int RS = D + 8;
+                float* big = reinterpret_cast<float*>(smem);  // [4][8][RS]
+                float* dst = big + (warp * kHeadsPerCta + g) * RS + 2 * t;
 #pragma unroll
-            for (int ps = 0; ps < D / 32; ++ps) {
-                float* dst = wpart + (warp * kHeadsPerCta + g) * 32;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int nt = 4 * ps + j;
-                    *reinterpret_cast<float2*>(dst + 8 * j + 2 * t) =
-                        make_float2(o[nt][0] + o[nt][2], o[nt][1] + o[nt][3]);
-                }
+                for (int nt = 0; nt < NT; ++nt)
+                    *reinterpret_cast<float2*>(dst + 8 * nt) = make_float2(o[nt][0] + o[nt][2], o[nt][1] + o[nt][3]);
                 __syncthreads();
-                for (int idx = tid; idx < kHeadsPerCta * 32; idx += kDecodeThreads) {
-                    const int h = idx >> 5, c = idx & 31;
+                for (int idx = tid; idx < kHeadsPerCta * D; idx += kDecodeThreads) {
+                    const int h = idx / D, c = idx % D;
                     float M = -INFINITY;
 #pragma unroll
                     for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, wm[w * kHeadsPerCta + h]);
@@ -488,12 +458,40 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                         for (int w = 0; w < kDecodeWarps; ++w) {
                             const float mw = wm[w * kHeadsPerCta + h];
                             const float a = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-                            O += a * wpart[(w * kHeadsPerCta + h) * 32 + c];
+                            O += a * big[(w * kHeadsPerCta + h) * RS + c];
                         }
                     }
-                    fo[h * D + 32 * ps + c] = O;
+                    fo[idx] = O;
                 }
-                __syncthreads();
+            } else {
+#pragma unroll
+                for (int ps = 0; ps < D / 32; ++ps) {
+                    float* dst = wpart + (warp * kHeadsPerCta + g) * 32;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int nt = 4 * ps + j;
+                        *reinterpret_cast<float2*>(dst + 8 * j + 2 * t) =
+                            make_float2(o[nt][0] + o[nt][2], o[nt][1] + o[nt][3]);
+                    }
+                    __syncthreads();
+                    for (int idx = tid; idx < kHeadsPerCta * 32; idx += kDecodeThreads) {
+                        const int h = idx >> 5, c = idx & 31;
+                        float M = -INFINITY;
+#pragma unroll
+                        for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, wm[w * kHeadsPerCta + h]);
+                        float O = 0.f;
+                        if (M != -INFINITY) {
+#pragma unroll
+                            for (int w = 0; w < kDecodeWarps; ++w) {
+                                const float mw = wm[w * kHeadsPerCta + h];
+                                const float a = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
+                                O += a * wpart[(w * kHeadsPerCta + h) * 32 + c];
+                            }
+                        }
+                        fo[h * D + 32 * ps + c] = O;
+                    }
+                    __syncthreads();
+                }
             }
             if (tid < kHeadsPerCta) {
                 float M = -INFINITY;
@@ -520,8 +518,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 n_parts = last - first + 1;
                 part = blockIdx.x - first;
             }
+            // (at the end of the run the idle pipeline doubles as the merge's staging area)
             finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm, fl, flag,
-                                                         wscratch);
+                                                         wscratch, (p.early_tiles & 0x100u) && i + 1 == ntiles ? smem : nullptr,
+                                                         static_cast<uint32_t>(decode_pipe_bytes<D, STAGES>()));
             fresh = true;
         }
         advance(cc);

@@ -11,6 +11,7 @@
 //   - the attention step's position cross-check against the caller's
 //     Cache::position(): crates/cpu-compute/src/cpu.rs:558-581.
 #include <atomic>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -112,7 +113,18 @@ struct itk_backend {
     bool gth_wait = true;  // ITK_GATHER_WAIT=0: do not check the peers' previous launch at kernel start
     int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
     bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
-    uint32_t l2_prefetch = 0; // ITK_DECODE_L2_PREFETCH: tiles per CTA the resident decode kernel requests into L2 before its wait
+    uint32_t early_tiles = 8; // ITK_DECODE_EARLY_TILES: tiles each warp pipeline requests before the dependency wait (up to its depth)
+    // attention preparation (per-head RMSNorm + rotary rotation), configured per layer
+    struct LayerPrep {
+        bool set = false;
+        float* q_w = nullptr;       // device [head_dim] or null
+        float* k_w = nullptr;
+        double* inv_freq = nullptr; // device [rotary_dim / 2] or null
+        float eps = 0.f;
+        uint32_t rotary_dim = 0, pairing = 0;
+    };
+    std::vector<LayerPrep> prep;
+    float *d_qp = nullptr, *d_kp = nullptr;  // prepared rows, stage_rows each (allocated with the first config)
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append, 2 = snapshot gather / restore scatter
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
@@ -609,7 +621,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
     if (const char* env = std::getenv("ITK_GATHER_WAIT")) b->gth_wait = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_DECODE_L2_PREFETCH")) b->l2_prefetch = static_cast<uint32_t>(std::atoi(env));
+    if (const char* env = std::getenv("ITK_DECODE_EARLY_TILES")) b->early_tiles = static_cast<uint32_t>(std::atoi(env));
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_VERIFY_TC")) b->verify_tc = std::atoi(env) != 0;
@@ -624,6 +636,13 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->k_slab);
     cudaFree(b->v_slab);
     cudaFree(b->tickets);
+    for (auto& lp : b->prep) {
+        cudaFree(lp.q_w);
+        cudaFree(lp.k_w);
+        cudaFree(lp.inv_freq);
+    }
+    cudaFree(b->d_qp);
+    cudaFree(b->d_kp);
     cudaFree(b->part_o);
     cudaFree(b->part_ml);
     cudaFree(b->d_q);
@@ -731,6 +750,32 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
         return true;
     };
     while (ctas > 1 && !fits(ctas)) --ctas;
+    // With dependent launch the next layer's CTAs move in as this layer's move out, and the CTAs that merge a
+    // cell (one per cell) move out last: the CTAs that inherit their places start late, finish late and become the
+    // next mergers.  When the plan is cell-aligned, leave one place per cell unused if that lengthens the runs by
+    // less than a twelfth, so that every CTA of the next layer finds a place before the merges begin.
+    if (b->use_pdl && b->forced_ctas <= 0 && cells < ctas) {
+        std::vector<uint32_t> keys(n_seqs), first(n_seqs + 1);
+        auto plan = [&](uint64_t g, uint32_t* worst, uint32_t* used) {
+            uint64_t total = 0;
+            for (uint32_t i = 0; i < n_seqs; ++i) {
+                uint64_t n = static_cast<uint64_t>(states[i].pos) + 1;
+                if (b->window[0] && n > b->window[0]) n = b->window[0];
+                keys[i] = static_cast<uint32_t>(n);
+                total += (n + 63) / 64 * HY;
+            }
+            const uint32_t per = static_cast<uint32_t>((total + g - 1) / g);
+            const bool ok = itk::decode_aligned_plan(keys.data(), n_seqs, HY, static_cast<uint32_t>(g),
+                                                     static_cast<uint32_t>(total), per, static_cast<uint32_t>(cap),
+                                                     first.data(), worst);
+            *used = first[n_seqs];
+            return ok;
+        };
+        uint32_t w0 = 0, u0 = 0, w1 = 0, u1 = 0;
+        if (plan(ctas, &w0, &u0) && ctas - u0 < cells && plan(ctas - cells, &w1, &u1) && fits(ctas - cells) &&
+            12ull * w1 <= 13ull * w0)
+            ctas -= cells;
+    }
     ITK_CUDA(b, cudaMemcpyAsync(b->d_states, states.data(), n_seqs * sizeof(itk::SeqState), cudaMemcpyHostToDevice,
                                 b->stream), "sequence-state upload");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
@@ -810,7 +855,7 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     }
     // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
     // the same layer) the kernel waits first.
-    p.l2_prefetch = b->l2_prefetch;
+    p.early_tiles = b->early_tiles;
     p.pdl = !b->use_pdl ? 0u : ((b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer) ? 2u : 1u);
     ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
              "resident decode launch");
@@ -987,6 +1032,133 @@ int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const u
     ITK_CUDA(b, cudaMemcpyAsync(b->d_v, v, kb, cudaMemcpyHostToDevice, b->stream), "v upload");
     ITK_CUDA(b, cudaMemcpyAsync(b->d_q, q, qb, cudaMemcpyHostToDevice, b->stream), "q upload");
     if (int rc = step_device(b, layer, n_seqs, slots, positions, rows, b->d_q, b->d_k, b->d_v, b->d_out)) return rc;
+    ITK_CUDA(b, cudaMemcpyAsync(out, b->d_out, qb, cudaMemcpyDeviceToHost, b->stream), "output download");
+    queue_status_read(b);
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention");
+    return check_status(b);
+}
+
+int itk_layer_prep_set(itk_backend* b, uint32_t layer, const itk_prep_config* cfg) {
+    if (!b || !cfg) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (int rc = check_layer(b, layer)) return rc;
+    const uint32_t D = b->cfg.head_dim;
+    if (D > 256) return b->fail(ITK_ERR_CAPACITY, "attention preparation: head_dim " + zu(D) + " exceeds 256");
+    // crates/torch-math/src/norm.rs:34-40, rope_interleaved.rs:72-95: the same refusals, by name
+    if ((cfg->q_norm_weight || cfg->k_norm_weight) && !(std::isfinite(cfg->norm_eps) && cfg->norm_eps > 0.f))
+        return b->fail(ITK_ERR_STEP_FAILED, "rms_norm: eps must be finite and > 0");
+    if (cfg->rotary_dim != 0) {
+        if (D < 2 || D % 2 != 0) return b->fail(ITK_ERR_STEP_FAILED, "rope: head_dim must be even and >= 2");
+        if (cfg->rotary_dim < 2 || cfg->rotary_dim % 2 != 0 || cfg->rotary_dim > D)
+            return b->fail(ITK_ERR_STEP_FAILED, "rope: rotary_dim must be even, >= 2, and <= head_dim");
+        if (!std::isfinite(cfg->rope_base) || cfg->rope_base <= 1.0f)
+            return b->fail(ITK_ERR_STEP_FAILED, "rope: base must be finite and > 1");
+        if (cfg->pairing > 1) return b->fail(ITK_ERR_INVALID_ARGUMENT, "rope: pairing is 0 (adjacent) or 1 (half split)");
+    }
+    if (b->prep.empty()) b->prep.resize(b->cfg.n_layers);
+    if (!b->d_qp) {
+        ITK_CUDA(b, cudaMalloc(&b->d_qp, b->stage_rows * b->q_width() * sizeof(float)), "prepared-row staging");
+        ITK_CUDA(b, cudaMalloc(&b->d_kp, b->stage_rows * b->row_len() * sizeof(float)), "prepared-row staging");
+    }
+    itk_backend::LayerPrep next;
+    auto upload = [&](const float* host, float** dev) -> int {
+        if (!host) return ITK_OK;
+        ITK_CUDA(b, cudaMalloc(dev, D * sizeof(float)), "norm weight allocation");
+        ITK_CUDA(b, cudaMemcpy(*dev, host, D * sizeof(float), cudaMemcpyHostToDevice), "norm weight upload");
+        return ITK_OK;
+    };
+    int rc = upload(cfg->q_norm_weight, &next.q_w);
+    if (rc == ITK_OK) rc = upload(cfg->k_norm_weight, &next.k_w);
+    if (rc == ITK_OK && cfg->rotary_dim != 0) {
+        // base^(-2i / rotary_dim) in f64, the CPU reference's own expression
+        std::vector<double> inv(cfg->rotary_dim / 2);
+        for (uint32_t i = 0; i < cfg->rotary_dim / 2; ++i)
+            inv[i] = std::pow(static_cast<double>(cfg->rope_base),
+                              -static_cast<double>(2 * i) / static_cast<double>(cfg->rotary_dim));
+        cudaError_t e = cudaMalloc(&next.inv_freq, inv.size() * sizeof(double));
+        if (e == cudaSuccess)
+            e = cudaMemcpy(next.inv_freq, inv.data(), inv.size() * sizeof(double), cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) rc = b->cuda_fail(e, "inverse-frequency table upload");
+    }
+    if (rc != ITK_OK) {
+        cudaFree(next.q_w);
+        cudaFree(next.k_w);
+        cudaFree(next.inv_freq);
+        return rc;
+    }
+    next.set = true;
+    next.eps = cfg->norm_eps;
+    next.rotary_dim = cfg->rotary_dim;
+    next.pairing = cfg->pairing;
+    itk_backend::LayerPrep& cur = b->prep[layer];
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention preparation");  // nothing in flight reads the old tables
+    cudaFree(cur.q_w);
+    cudaFree(cur.k_w);
+    cudaFree(cur.inv_freq);
+    cur = next;
+    return ITK_OK;
+}
+
+// Prepares the call's Q and K rows (device f32) into the backend's staging, then runs the ordinary step on them.
+static int step_prepared(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                         const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
+                         const float* d_v, float* d_out) {
+    if (int rc = check_layer(b, layer)) return rc;
+    if (b->prep.empty() || !b->prep[layer].set)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "attention preparation: layer " + zu(layer) +
+                                                     " has no configuration (itk_layer_prep_set)");
+    std::vector<SeqDesc> seqs;
+    if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
+    const size_t total_rows = static_cast<size_t>(n_seqs) * rows;
+    if (total_rows > b->stage_rows)
+        return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(total_rows) + " rows exceed the staging capacity of " +
+                                             zu(b->stage_rows));
+    const itk_backend::LayerPrep& lp = b->prep[layer];
+    itk::PrepLaunch p{};
+    p.q_in = d_q;
+    p.k_in = d_k;
+    p.q_out = b->d_qp;
+    p.k_out = b->d_kp;
+    p.q_w = lp.q_w;
+    p.k_w = lp.k_w;
+    p.inv_freq = lp.inv_freq;
+    p.eps = lp.eps;
+    p.rotary_dim = lp.rotary_dim;
+    p.pairing = lp.pairing;
+    p.q_heads = b->cfg.q_heads;
+    p.kv_heads = b->cfg.kv_heads;
+    p.head_dim = b->cfg.head_dim;
+    p.rows = rows;
+    p.n_seqs = n_seqs;
+    for (uint32_t i = 0; i < n_seqs; ++i) p.pos0[i] = static_cast<uint32_t>(positions[i]);
+    ITK_CUDA(b, itk::launch_prep(p, b->stream, &b->stats.kernel_launches), "attention preparation launch");
+    return step_device(b, layer, n_seqs, slots, positions, rows, b->d_qp, b->d_kp, d_v, d_out);
+}
+
+int itk_attention_batch_prep_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                                    const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
+                                    const float* d_v, float* d_out) {
+    if (!b || !slots || !positions || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    return step_prepared(b, layer, n_seqs, slots, positions, rows, d_q, d_k, d_v, d_out);
+}
+
+int itk_attention_batch_prep(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
+                             const uint64_t* positions, uint32_t rows, const float* q, const float* k, const float* v,
+                             float* out) {
+    if (!b || !slots || !positions || !q || !k || !v || !out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    std::vector<SeqDesc> seqs;
+    if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
+    const size_t total_rows = static_cast<size_t>(n_seqs) * rows;
+    if (total_rows > b->stage_rows)
+        return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(total_rows) + " rows exceed the staging capacity of " +
+                                             zu(b->stage_rows));
+    const size_t qb = total_rows * b->q_width() * sizeof(float), kb = total_rows * b->row_len() * sizeof(float);
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_k, k, kb, cudaMemcpyHostToDevice, b->stream), "k upload");
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_v, v, kb, cudaMemcpyHostToDevice, b->stream), "v upload");
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_q, q, qb, cudaMemcpyHostToDevice, b->stream), "q upload");
+    if (int rc = step_prepared(b, layer, n_seqs, slots, positions, rows, b->d_q, b->d_k, b->d_v, b->d_out)) return rc;
     ITK_CUDA(b, cudaMemcpyAsync(out, b->d_out, qb, cudaMemcpyDeviceToHost, b->stream), "output download");
     queue_status_read(b);
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention");

@@ -91,8 +91,7 @@ struct AttnLaunch {
     uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
-    uint32_t l2_prefetch;    // decode kernel with pdl == 2: 64-key tiles of its run, beyond those it stages in shared
-                             // memory, that each CTA requests into L2 before it waits for the previous kernel
+    uint32_t early_tiles;    // decode kernel with pdl == 2: tiles per warp pipeline requested before the wait
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
@@ -126,6 +125,22 @@ struct AppendLaunch {
     const float* v_src;
     uint32_t ring, kv_heads, head_dim, rows, n_seqs;
     SeqDesc seq[kMaxSeqsPerLaunch];
+};
+
+// Attention preparation (per-head RMSNorm and rotary rotation of the Q and K rows of one call).
+struct PrepLaunch {
+    const float* q_in;       // [n_seqs][rows][q_heads][D]
+    const float* k_in;       // [n_seqs][rows][kv_heads][D]
+    float* q_out;            // same shapes; may not alias the inputs
+    float* k_out;
+    const float* q_w;        // [D] RMSNorm weight of the Q head rows, or null: no norm
+    const float* k_w;        // [D] ... of the K head rows, or null
+    const double* inv_freq;  // [rotary_dim / 2] base^(-2i / rotary_dim); null when rotary_dim == 0
+    float eps;
+    uint32_t rotary_dim;     // 0 = no rotation; even, <= head_dim
+    uint32_t pairing;        // 0 = adjacent pairs (2i, 2i + 1), 1 = half split (i, i + rotary_dim / 2)
+    uint32_t q_heads, kv_heads, head_dim, rows, n_seqs;
+    uint32_t pos0[kMaxSeqsPerLaunch];  // absolute position of each sequence's first row
 };
 
 // One layer of a snapshot gather / restore scatter.
@@ -172,6 +187,35 @@ cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t par
 // pdl != 0 launches with programmatic stream serialization (see AttnLaunch::pdl).
 // pos += 1 for the first n states.
 cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, uint64_t* launches);
+// The decode kernel's cell-aligned plan: every cell (sequence s has `cells_per_seq` of them, each of
+// tiles(keys[s]) 64-key tiles) gets floor(G * T / total) CTAs of its own and equal runs inside it.  Returns
+// whether that plan is taken - every cell gets at least one CTA, no cell needs more than `splits` parts and the
+// longest run exceeds `per` (the equal-run length of the unaligned plan) by at most a sixteenth - and fills
+// first_cta[0..n_seqs] (first CTA of each sequence's cells), *worst (longest run in tiles).  Evaluated by the kernel
+// and, identically, by the host when it sizes the grid.
+__host__ __device__ inline bool decode_aligned_plan(const uint32_t* keys, uint32_t n_seqs, uint32_t cells_per_seq,
+                                                    uint32_t G, uint32_t total, uint32_t per, uint32_t splits,
+                                                    uint32_t* first_cta, uint32_t* worst) {
+    bool ok = total >= G && G > 0;
+    uint32_t b = 0, w = 0;
+    for (uint32_t s = 0; s < n_seqs && ok; ++s) {
+        const uint32_t T = (keys[s] + 63u) / 64u;
+        const uint32_t ns = static_cast<uint32_t>(static_cast<unsigned long long>(T) * G / total);  // CTAs per cell
+        if (ns == 0) {
+            ok = false;
+            break;
+        }
+        const uint32_t run = (T + ns - 1) / ns;
+        if ((T + run - 1) / run > splits) ok = false;  // more parts than the scratch has slots per cell
+        if (run > w) w = run;
+        first_cta[s] = b;
+        b += ns * cells_per_seq;
+    }
+    first_cta[n_seqs] = b;
+    *worst = w;
+    const uint32_t slack = per / 16u > 1u ? per / 16u : 1u;
+    return ok && w <= per + slack;
+}
 // Most CTAs that can share a cell of T tiles when every CTA walks `per` tiles.
 inline uint32_t decode_parts_for(uint32_t T, uint32_t per) { return (T + per - 2) / per + 1; }
 bool decode_f16_supported(uint32_t head_dim, uint32_t rows);
@@ -188,6 +232,7 @@ cudaError_t configure_verify_tc();
 // General kernel: any head_dim <= 256, any rows, f32 or f16 cache (CUDA cores, f32 math).
 cudaError_t launch_attn_general(const AttnLaunch& p, bool f16, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_snapshot_copy(const CopyLaunch& p, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_prep(const PrepLaunch& p, cudaStream_t s, uint64_t* launches);
 // One-time per-device kernel attribute setup (dynamic shared memory opt-in).
 cudaError_t configure_kernels();
 

@@ -182,6 +182,24 @@ inline Status rope_interleaved_partial(const float* in, size_t len, size_t posit
     return {};
 }
 
+// RMSNorm with a weight vector. Follows crates/torch-math/src/norm.rs:21-53: the mean of squares is summed
+// in f64 in element order, inv_rms = 1 / sqrt(mean + eps) in f64, and each output is
+// (f64(v) * inv_rms * f64(w)) rounded once to f32.  Refusals in the reference's order: empty input, weight
+// length, eps not finite and > 0.
+inline Status rms_norm(const float* in, size_t len, const float* weight, size_t weight_len, float eps, float* out) {
+    if (len == 0) return Status::fail(kStepFailed, "rms_norm: input is empty");
+    if (weight_len != len)
+        return Status::fail(kShapeMismatch, "rms_norm: got " + zu(weight_len) + ", expected " + zu(len));
+    if (!std::isfinite(eps) || eps <= 0.0f) return Status::fail(kStepFailed, "rms_norm: eps must be finite and > 0");
+    double sum = 0.0;
+    for (size_t i = 0; i < len; ++i) sum += static_cast<double>(in[i]) * static_cast<double>(in[i]);
+    const double mean_sq = sum / static_cast<double>(len);
+    const double inv_rms = 1.0 / std::sqrt(mean_sq + static_cast<double>(eps));
+    for (size_t i = 0; i < len; ++i)
+        out[i] = static_cast<float>(static_cast<double>(in[i]) * inv_rms * static_cast<double>(weight[i]));
+    return {};
+}
+
 // Half-split (NeoX) rotation. Follows crates/torch-math/src/rope.rs:63-117:
 // pair i joins channel i with channel i + rotary_dim/2, same f64 angle law.
 inline Status rope_half_partial(const float* in, size_t len, size_t position, float base,
@@ -1175,5 +1193,72 @@ class CpuBackend {
     std::unique_ptr<KvCache> cache_;
     std::optional<BackendConfig> shape_;
 };
+
+// ---------------------------------------------------------------------------
+// Draft-model (DFlash) attention.  Follows crates/dflash/src/model.rs:388-466: for query row r at positions[r],
+// the visible set is the committed rows in ascending position order, then the block's own rows in order, each
+// kept unless (causal and kp > p) or (sliding and kp <= p - window, signed); per query head: scores = dot * scale
+// with scale = 1 / sqrt(key_len as f32) (sequential f32 dot, :585-587), max, e = exp(s - max) summed in order,
+// out += (e / sum) * v.  `committed_k` / `committed_v` are compact here ([committed][kv_heads * len], in the order
+// of `committed_positions`), as the CPU cache's map iteration yields them (crates/dflash/src/cache.rs:96-104).
+inline Status draft_attention(const float* q, size_t rows, size_t q_heads, size_t kv_heads, size_t key_len,
+                              size_t value_len, const uint64_t* positions, const uint64_t* committed_positions,
+                              size_t committed, const float* committed_k, const float* committed_v,
+                              const float* block_k, const float* block_v, bool causal, bool sliding, uint64_t window,
+                              float* out) {
+    if (q_heads == 0 || kv_heads == 0 || q_heads % kv_heads != 0)
+        return Status::fail(kNonDivisibleHeads, "q_heads " + zu(q_heads) + " must be a whole multiple of kv_heads " +
+                                                    zu(kv_heads) + ", both non-zero");
+    if (key_len == 0 || value_len == 0) return Status::fail(kZeroDimension, "key_len / value_len is zero");
+    const size_t group = q_heads / kv_heads;
+    const size_t k_w = kv_heads * key_len, v_w = kv_heads * value_len;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(key_len));
+    for (size_t i = 0; i < rows * q_heads * value_len; ++i) out[i] = 0.0f;
+    std::vector<std::pair<const float*, const float*>> visible;
+    std::vector<float> scores;
+    for (size_t r = 0; r < rows; ++r) {
+        const int64_t p = static_cast<int64_t>(positions[r]);
+        const int64_t w = static_cast<int64_t>(window);
+        visible.clear();
+        for (size_t c = 0; c < committed; ++c) {
+            const int64_t kp = static_cast<int64_t>(committed_positions[c]);
+            if (causal && kp > p) continue;
+            if (sliding && kp <= p - w) continue;
+            visible.emplace_back(committed_k + c * k_w, committed_v + c * v_w);
+        }
+        for (size_t m = 0; m < rows; ++m) {
+            const int64_t mp = static_cast<int64_t>(positions[m]);
+            if (causal && mp > p) continue;
+            if (sliding && mp <= p - w) continue;
+            visible.emplace_back(block_k + m * k_w, block_v + m * v_w);
+        }
+        for (size_t head = 0; head < q_heads; ++head) {
+            const size_t kv_head = head / group;
+            const float* qh = q + (r * q_heads + head) * key_len;
+            scores.clear();
+            float max = -INFINITY;
+            for (const auto& kv : visible) {
+                const float* kh = kv.first + kv_head * key_len;
+                float dot = 0.0f;
+                for (size_t d = 0; d < key_len; ++d) dot += qh[d] * kh[d];
+                const float s = dot * scale;
+                if (s > max) max = s;
+                scores.push_back(s);
+            }
+            float sum = 0.0f;
+            for (float& s : scores) {
+                s = std::exp(s - max);
+                sum += s;
+            }
+            float* o = out + (r * q_heads + head) * value_len;
+            for (size_t i = 0; i < visible.size(); ++i) {
+                const float weight = scores[i] / sum;
+                const float* vh = visible[i].second + kv_head * value_len;
+                for (size_t d = 0; d < value_len; ++d) o[d] += weight * vh[d];
+            }
+        }
+    }
+    return {};
+}
 
 }  // namespace orc

@@ -218,6 +218,52 @@ def rope_rows(x, heads: int, head_dim: int, start_position: int, base: float, pa
     return out
 
 
+def rms_norm(x, weight, eps: float) -> np.ndarray:
+    """torch_math::rms_norm (crates/torch-math/src/norm.rs:21-53) over one row."""
+    a, w = _f32(x).reshape(-1), _f32(weight).reshape(-1)
+    out = np.empty(max(a.size, 1), dtype=np.float32)
+    _check(lib().orc_rms_norm(_fp(a), _sz(a.size), _fp(w), _sz(w.size), C.c_float(eps), _fp(out)))
+    return out[:a.size]
+
+
+def prepare_rows(x, heads: int, head_dim: int, start_position: int, weight=None, eps: float = 1e-6,
+                 rope_base: Optional[float] = None, rotary_dim: Optional[int] = None, pairing: int = 0) -> np.ndarray:
+    """The attention preparation of ``[rows][heads][head_dim]`` rows as the reference composes it: per-head
+    rms_norm (when a weight is given), then the rotation of each head row at its position (when a base is given;
+    crates/wgpu-compute/src/kernels/k9_attn_prep.rs:1-40 states the composition, the CPU functions do the math)."""
+    a = _f32(x).reshape(-1, heads, head_dim).copy()
+    for r in range(a.shape[0]):
+        for h in range(heads):
+            row = a[r, h]
+            if weight is not None:
+                row = rms_norm(row, weight, eps)
+            if rope_base is not None:
+                fn = rope_interleaved if pairing == 0 else rope
+                row = fn(row, start_position + r, rope_base, head_dim, rotary_dim)
+            a[r, h] = row
+    return a
+
+
+def draft_attention(q, positions, committed_positions, committed_k, committed_v, block_k, block_v, q_heads: int,
+                    kv_heads: int, key_len: int, value_len: int, causal: bool = False, sliding: bool = False,
+                    window: int = 0) -> np.ndarray:
+    """The draft model's attention over committed + block rows (crates/dflash/src/model.rs:388-466).
+    ``committed_k`` / ``committed_v`` are compact ``[committed][kv_heads*len]`` in the order of
+    ``committed_positions``; returns ``[rows][q_heads*value_len]``."""
+    q = _f32(q).reshape(-1)
+    rows = len(positions)
+    ck, cv = _f32(committed_k).reshape(-1), _f32(committed_v).reshape(-1)
+    bk, bv = _f32(block_k).reshape(-1), _f32(block_v).reshape(-1)
+    pos = np.ascontiguousarray(positions, dtype=np.uint64)
+    cpos = np.ascontiguousarray(committed_positions, dtype=np.uint64)
+    out = np.zeros(max(rows * q_heads * value_len, 1), dtype=np.float32)
+    u64p = C.POINTER(C.c_uint64)
+    _check(lib().orc_draft_attention(_fp(q), _sz(rows), _sz(q_heads), _sz(kv_heads), _sz(key_len), _sz(value_len),
+                                     pos.ctypes.data_as(u64p), cpos.ctypes.data_as(u64p), _sz(len(cpos)), _fp(ck), _fp(cv),
+                                     _fp(bk), _fp(bv), int(causal), int(sliding), C.c_uint64(window), _fp(out)))
+    return out[: rows * q_heads * value_len].reshape(rows, q_heads * value_len)
+
+
 def default_scale(head_dim: int) -> float:
     return float(lib().orc_default_scale(_sz(head_dim)))
 

@@ -65,6 +65,16 @@ int orc_rope_rows(int pairing, const float* in, size_t rows, size_t heads, size_
         }
     return done({});
 }
+int orc_rms_norm(const float* in, size_t len, const float* weight, size_t weight_len, float eps, float* out) {
+    return done(rms_norm(in, len, weight, weight_len, eps, out));
+}
+int orc_draft_attention(const float* q, size_t rows, size_t q_heads, size_t kv_heads, size_t key_len, size_t value_len,
+                        const uint64_t* positions, const uint64_t* committed_positions, size_t committed,
+                        const float* committed_k, const float* committed_v, const float* block_k, const float* block_v,
+                        int causal, int sliding, uint64_t window, float* out) {
+    return done(draft_attention(q, rows, q_heads, kv_heads, key_len, value_len, positions, committed_positions, committed,
+                                committed_k, committed_v, block_k, block_v, causal != 0, sliding != 0, window, out));
+}
 float orc_default_scale(size_t head_dim) { return default_scale(head_dim); }
 int orc_kv_head_for_query_head(size_t q_head, size_t hq, size_t hkv, size_t* out) {
     return done(kv_head_for_query_head(q_head, hq, hkv, out));
