@@ -34,7 +34,7 @@ extern "C" {
 #endif
 
 /* Refusal codes.  1..14 mirror crates/attention/src/error.rs:9-127
- * (AttentionError), 32..39 mirror crates/itak-kv/src/error.rs (KvError),
+ * (AttentionError), 32..46 mirror crates/itak-kv/src/error.rs (KvError),
  * 64 is the backend's own StepFailed{step, detail}
  * (crates/cpu-compute/src/cpu.rs:28-33).  100+ have no counterpart: they are
  * limits of a device-resident cache with a fixed allocation. */
@@ -62,6 +62,13 @@ typedef enum itk_status {
     ITK_ERR_CHECKSUM_MISMATCH = 37,
     ITK_ERR_GEOMETRY_MISMATCH = 38,
     ITK_ERR_FINGERPRINT_MISMATCH = 39,
+    ITK_ERR_EMPTY_PREFIX = 40,
+    ITK_ERR_TOKEN_COUNT_MISMATCH = 41,
+    ITK_ERR_PREFIX_HASH_MISMATCH = 42,
+    ITK_ERR_SNAPSHOT_TOKEN_MISMATCH = 43,
+    ITK_ERR_ENTRY_TOO_LARGE = 44,
+    ITK_ERR_INVALID_CONFIG = 45,
+    ITK_ERR_IO = 46,
     ITK_ERR_STEP_FAILED = 64,
     ITK_ERR_CUDA = 100,
     ITK_ERR_INVALID_ARGUMENT = 101,
@@ -370,6 +377,40 @@ int itk_decode_attention_noalloc(const void* k_layer, const void* v_layer, uint3
                                  uint32_t q_heads, uint32_t head_dim, uint32_t n_seqs, const uint32_t* slots,
                                  const uint32_t* kv_len, const float* d_q, float* d_out, uint32_t splits,
                                  void* cuda_stream, char* error_text, size_t error_text_len);
+
+/* ---- the persistent prefix store ------------------------------------------------ */
+
+/* PrefixStore (crates/itak-kv/src/store.rs): one file per entry under `root`, keyed by token prefix, bounded by
+ * `max_bytes` with least-recently-used eviction; same entry bytes and file names as the reference's store (layout
+ * store.rs:5-21), so a directory can be shared with it.  Host code only.  An entry's payload is a snapshot in the
+ * ITKV encoding (itk_snapshot_to_itkv / itk_snapshot_from_itkv).  Calls on one store are serialised by the caller.
+ *   open     store.rs:147-170: refuses a zero cap (ITK_ERR_INVALID_CONFIG), creates the root, indexes every
+ *            well-formed "*.kv" entry; malformed files are left on disk, unindexed, and named by
+ *            itk_prefix_store_last_refusal.  itk_prefix_store_last_error(NULL) has the text of a failed open.
+ *   put      store.rs:236-303: refuses an empty prefix, a snapshot whose token count differs from the id count, an
+ *            entry larger than the cap; writes a temp file, syncs, renames; then evicts least recently used entries
+ *            (never the new one) until the store is within its cap.  `now` is the caller's clock (unix seconds).
+ *   lookup   store.rs:314-452: the longest stored prefix of `query` that passes every trust check - ids hash back
+ *            to the key, ids equal the query's prefix, payload decodes whole and covers the preamble's token count,
+ *            and, when given, the required geometry (n_layers, layer_window, kv_heads, head_dim of an itk_config)
+ *            and fingerprint match.  A candidate that fails is refused by name and the search goes on to shorter
+ *            prefixes.  A hit restamps the entry's last-used time in place.  *token_count == 0 is a clean miss;
+ *            the returned bytes belong to the store until its next call. */
+typedef struct itk_prefix_store itk_prefix_store;
+int itk_prefix_store_open(const char* root, uint64_t max_bytes, itk_prefix_store** out);
+void itk_prefix_store_close(itk_prefix_store* s);
+const char* itk_prefix_store_last_error(const itk_prefix_store* s);
+const char* itk_prefix_store_last_refusal(const itk_prefix_store* s);
+int itk_prefix_store_rescan(itk_prefix_store* s);
+int itk_prefix_store_put(itk_prefix_store* s, const uint32_t* tokens, size_t n_tokens, const uint8_t* itkv, size_t itkv_len,
+                         uint64_t now);
+int itk_prefix_store_lookup(itk_prefix_store* s, const uint32_t* query, size_t n_query, const itk_config* required_geometry,
+                            const char* required_fingerprint, uint64_t now, uint64_t* token_count, const uint8_t** itkv,
+                            size_t* itkv_len);
+int itk_prefix_store_stats(const itk_prefix_store* s, uint64_t* entries, uint64_t* total_bytes, uint64_t* max_bytes);
+/* Entry `i` of the index, longest prefix first (store.rs:179-184). */
+int itk_prefix_store_entry(const itk_prefix_store* s, uint64_t i, char* file_name, size_t file_name_cap, uint64_t* prefix_hash,
+                           uint64_t* token_count, uint64_t* bytes, uint64_t* created_unix, uint64_t* last_used_unix);
 
 #ifdef __cplusplus
 }

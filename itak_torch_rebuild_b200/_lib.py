@@ -31,6 +31,13 @@ ERR_TRUNCATED = 36
 ERR_CHECKSUM_MISMATCH = 37
 ERR_GEOMETRY_MISMATCH = 38
 ERR_FINGERPRINT_MISMATCH = 39
+ERR_EMPTY_PREFIX = 40
+ERR_TOKEN_COUNT_MISMATCH = 41
+ERR_PREFIX_HASH_MISMATCH = 42
+ERR_SNAPSHOT_TOKEN_MISMATCH = 43
+ERR_ENTRY_TOO_LARGE = 44
+ERR_INVALID_CONFIG = 45
+ERR_IO = 46
 ERR_STEP_FAILED = 64
 ERR_CUDA = 100
 ERR_INVALID_ARGUMENT = 101
@@ -141,6 +148,16 @@ SIGNATURES = {
     "itk_snapshot_from_itkv": (C.c_int, [_vp, C.c_char_p, _sz, C.c_char_p, C.POINTER(_vp)]),
     "itk_draft_attention": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
                                       _u32, _u32, C.c_float, _vp, _vp, C.c_char_p, _sz]),
+    "itk_prefix_store_open": (C.c_int, [C.c_char_p, _u64, C.POINTER(_vp)]),
+    "itk_prefix_store_close": (None, [_vp]),
+    "itk_prefix_store_last_error": (C.c_char_p, [_vp]),
+    "itk_prefix_store_last_refusal": (C.c_char_p, [_vp]),
+    "itk_prefix_store_rescan": (C.c_int, [_vp]),
+    "itk_prefix_store_put": (C.c_int, [_vp, _u32p, _sz, _vp, _sz, _u64]),
+    "itk_prefix_store_lookup": (C.c_int, [_vp, _u32p, _sz, C.POINTER(Config), C.c_char_p, _u64, _u64p, C.POINTER(_vp),
+                                          C.POINTER(_sz)]),
+    "itk_prefix_store_stats": (C.c_int, [_vp, _u64p, _u64p, _u64p]),
+    "itk_prefix_store_entry": (C.c_int, [_vp, _u64, C.c_char_p, _sz, _u64p, _u64p, _u64p, _u64p, _u64p]),
     "itk_decode_attention_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _vp, _vp, _u32, _vp,
                                                C.c_char_p, _sz]),
 }

@@ -110,6 +110,17 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar_addr, uint32_t parity
     return false;
 }
 
+// Timeline stamps of CTA (0, 0, 0) (compiled in only with -DITK_DECODE_TRACE): SM clock per role and tile.
+#ifdef ITK_DECODE_TRACE
+#define TC_TRACE(p, slot)                                                                              \
+    do {                                                                                               \
+        if ((p).trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512)         \
+            (p).trace[(slot)] = static_cast<unsigned long long>(clock64());                            \
+    } while (0)
+#else
+#define TC_TRACE(p, slot) do { } while (0)
+#endif
+
 // PC = pairs per CTA (32 or 64).
 template <int PC>
 __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_constant__ AttnLaunch p) {
@@ -160,6 +171,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t span = k1 - k0;
     const uint32_t ntiles = (span + kTcTile - 1) / kTcTile;
 
+    if (tid == 0) TC_TRACE(p, 256);
     if (tid == 0) {
         for (int s = 0; s < kTcStagesK; ++s) {
             tc::mbar_init(bar_full_k + 8 * s, kTcLoaderThreads);
@@ -258,6 +270,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             }
             // The stage's full barrier receives this thread's arrival when the copies above have landed; nobody waits.
             cp_async_arrive_noinc(bar_full + 8 * st);
+            if (lt == 0) TC_TRACE(p, tile * 8 + (is_v ? 6 : 5));
         }
         cp_async_wait_all();
     } else if (warp == kTcMmaWarp) {
@@ -288,7 +301,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             if (wait_or_abort(bar_q, 0u, abort_flag) && wait_or_abort(bar_full_k, 0u, abort_flag)) {
                 tc::fence_proxy_async();  // the tile was written through the generic proxy (cp.async)
                 tc::fence_after_sync();
+                TC_TRACE(p, 0);
                 issue_qk(0);
+                TC_TRACE(p, 7);
                 for (uint32_t tile = 0; tile < ntiles; ++tile) {
                     if (*abort_flag != 0) break;
                     if (tile + 1 < ntiles) {
@@ -300,13 +315,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                         if (!wait_or_abort(bar_sfree, tile & 1u, abort_flag)) break;
                         tc::fence_proxy_async();
                         tc::fence_after_sync();
+                        TC_TRACE(p, (tile + 1) * 8 + 0);
                         issue_qk(tile + 1);
+                        TC_TRACE(p, (tile + 1) * 8 + 7);
                     }
                     if (!wait_or_abort(bar_p + 8 * (tile & 1u), (tile >> 1) & 1u, abort_flag)) break;
                     if (!wait_or_abort(bar_full_v + 8 * (tile % kTcStagesV), (tile / kTcStagesV) & 1u, abort_flag)) break;
                     tc::fence_proxy_async();
                     tc::fence_after_sync();
+                    TC_TRACE(p, tile * 8 + 1);
                     issue_pv(tile);
+                    TC_TRACE(p, tile * 8 + 2);
                 }
             }
         }
@@ -379,6 +398,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                 tc::tmem_st16(tmem + lane_base + kTmemQ + 16 * c, hi);
                 tc::tmem_st16(tmem + lane_base + kTmemQ + 64 + 16 * c, lo);
             }
+            if (tid == 0) TC_TRACE(p, 257);
             mbar_arrive(bar_go);  // (release) the staging area may be overwritten by the V stream
             // Both P buffers start as zeros: a row only ever writes its own columns.
             uint32_t z[16];
@@ -400,6 +420,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             // tile - 2, which read the P buffer this tile writes).
             if (!__all_sync(0xffffffffu, wait_or_abort(bar_s, tile & 1u, abort_flag))) { done = false; break; }
             tc::fence_after_sync();
+            if (tid == 0) TC_TRACE(p, tile * 8 + 3);
             const int32_t kr0 = static_cast<int32_t>(tile * kTcTile + col0);
             // Tiles wholly inside every row's visible range (all but the causal edge and a window's trailing edge)
             // skip the masks.
@@ -491,6 +512,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             }
             tc::tmem_wait_st();
             tc::fence_before_sync();
+            if (tid == 0) TC_TRACE(p, tile * 8 + 4);
             mbar_arrive(bar_p + 8 * (tile & 1u));  // weights stored
         }
         // The last two products: the scores of the last tile only vouch for those up to tile ntiles - 3.
@@ -621,6 +643,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     }
     tc::fence_before_sync();
     __syncthreads();
+    if (tid == 0) TC_TRACE(p, 258);
     if (tid == 0 && *abort_flag != 0 && p.status) atomicOr(p.status, 1u);
     if (warp == kTcMmaWarp) tc::tmem_dealloc(tmem, kTmemCols);
 }

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../../include/itak_cuda_compute.h"
+#include "itkv_codec.hpp"
 #include "kernels.cuh"
 
 namespace itk {
@@ -32,6 +33,10 @@ namespace {
 
 using itk::AppendLaunch;
 using itk::AttnLaunch;
+#ifdef ITK_DECODE_TRACE
+// Timeline build only: [layer][512 CTAs][16] stamps, allocated on request.
+static unsigned long long* g_trace = nullptr;
+#endif
 using itk::CopyLaunch;
 using itk::SeqDesc;
 
@@ -342,6 +347,9 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                 p.v_new = d_v_new + static_cast<size_t>(at) * rows * b->row_len();
             }
             b->status_pending = true;
+#ifdef ITK_DECODE_TRACE
+            p.trace = g_trace;
+#endif
             ITK_CUDA(b, itk::launch_verify_tc(p, b->stream, &b->stats.kernel_launches), "tensor-core attention launch");
             prof_end(b, ev);
             continue;
@@ -795,8 +803,6 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
 }
 
 #ifdef ITK_DECODE_TRACE
-// Timeline build only: [layer][512 CTAs][16] stamps, allocated on request.
-static unsigned long long* g_trace = nullptr;
 extern "C" int itk_debug_trace_buffer(void** dev_ptr, uint64_t* bytes) {
     const size_t n = 64ull * 512 * 16 * sizeof(unsigned long long);
     if (!g_trace) {
@@ -1668,18 +1674,6 @@ int itk_snapshot_from_host_f32(itk_backend* b, uint64_t token_count, const uint6
 // ---------------------------------------------------------------------------------------------------------
 namespace {
 
-constexpr uint64_t kFnvOffset = 0xcbf29ce484222325ull;  // crates/itak-kv/src/hash.rs:13-16
-constexpr uint64_t kFnvPrime = 0x00000100000001b3ull;
-
-uint64_t fnv1a64(const uint8_t* p, size_t n) {
-    uint64_t h = kFnvOffset;
-    for (size_t i = 0; i < n; ++i) {
-        h ^= p[i];
-        h *= kFnvPrime;
-    }
-    return h;
-}
-
 // Exact f16 -> f32 (crates/gguf/src/dequant.rs:12-34).
 float half_bits_to_float(uint16_t h) {
     const uint32_t sign = h >> 15, exp = (h >> 10) & 0x1f, frac = h & 0x3ff;
@@ -1708,55 +1702,7 @@ void put_u64(std::vector<uint8_t>& b, uint64_t v) {
     for (int i = 0; i < 8; ++i) b.push_back(static_cast<uint8_t>(v >> (8 * i)));
 }
 
-// Strict little-endian cursor (snapshot.rs:546-607).
-struct ItkvReader {
-    const uint8_t* bytes;
-    size_t len, at;
-    size_t remaining() const { return len - at; }
-    bool take(size_t n, const uint8_t** out) {
-        if (remaining() < n) return false;
-        *out = bytes + at;
-        at += n;
-        return true;
-    }
-    bool u32(uint32_t* v) {
-        const uint8_t* p;
-        if (!take(4, &p)) return false;
-        *v = 0;
-        for (int i = 0; i < 4; ++i) *v |= static_cast<uint32_t>(p[i]) << (8 * i);
-        return true;
-    }
-    bool u64(uint64_t* v) {
-        const uint8_t* p;
-        if (!take(8, &p)) return false;
-        *v = 0;
-        for (int i = 0; i < 8; ++i) *v |= static_cast<uint64_t>(p[i]) << (8 * i);
-        return true;
-    }
-};
-
-bool valid_utf8(const uint8_t* s, size_t n) {
-    size_t i = 0;
-    while (i < n) {
-        const uint8_t c = s[i];
-        size_t extra;
-        uint32_t cp;
-        if (c < 0x80) { ++i; continue; }
-        else if ((c & 0xe0) == 0xc0) { extra = 1; cp = c & 0x1f; }
-        else if ((c & 0xf0) == 0xe0) { extra = 2; cp = c & 0x0f; }
-        else if ((c & 0xf8) == 0xf0) { extra = 3; cp = c & 0x07; }
-        else return false;
-        if (i + extra >= n) return false;
-        for (size_t k = 1; k <= extra; ++k) {
-            if ((s[i + k] & 0xc0) != 0x80) return false;
-            cp = (cp << 6) | (s[i + k] & 0x3f);
-        }
-        if ((extra == 1 && cp < 0x80) || (extra == 2 && cp < 0x800) || (extra == 3 && cp < 0x10000)) return false;
-        if (cp > 0x10ffff || (cp >= 0xd800 && cp <= 0xdfff)) return false;
-        i += extra + 1;
-    }
-    return true;
-}
+using itk::itkv::fnv1a64;
 
 }  // namespace
 
@@ -1830,78 +1776,14 @@ int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* s, const char* mode
 int itk_snapshot_from_itkv(itk_backend* b, const uint8_t* bytes, size_t n, const char* expected_fingerprint,
                            itk_snapshot** out) {
     if (!b || !bytes || !out) return ITK_ERR_INVALID_ARGUMENT;
-    auto truncated = [&](const ItkvReader& r, size_t want) {
-        return b->fail(ITK_ERR_TRUNCATED, "snapshot: truncated, needed " + zu(r.at + want) + " bytes, have " + zu(r.len));
-    };
-    auto inconsistent = [&](std::string d) { return b->fail(ITK_ERR_INCONSISTENT_SNAPSHOT, "inconsistent snapshot: " + d); };
-    ItkvReader r{bytes, n, 0};
-    const uint8_t* p;
-    if (!r.take(4, &p)) return truncated(r, 4);
-    if (std::memcmp(p, "ITKV", 4) != 0) return b->fail(ITK_ERR_BAD_MAGIC, "snapshot: bad magic");
-    uint32_t version;
-    if (!r.u32(&version)) return truncated(r, 4);
-    if (version != 1) return b->fail(ITK_ERR_UNSUPPORTED_VERSION, "snapshot: unsupported format version " + zu(version));
-    uint32_t fp_len;
-    if (!r.u32(&fp_len)) return truncated(r, 4);
-    const uint8_t* fp;
-    if (!r.take(fp_len, &fp)) return truncated(r, fp_len);
-    if (!valid_utf8(fp, fp_len)) return inconsistent("model fingerprint is not valid UTF-8");
-    uint64_t token_count;
-    uint32_t hkv, hd, layer_count;
-    if (!r.u64(&token_count)) return truncated(r, 8);
-    if (!r.u32(&hkv)) return truncated(r, 4);
-    if (!r.u32(&hd)) return truncated(r, 4);
-    if (!r.u32(&layer_count)) return truncated(r, 4);
-    if (layer_count > r.remaining() / 28)
-        return inconsistent("snapshot declares " + zu(layer_count) + " layers but only " + zu(r.remaining()) +
-                            " bytes remain, not enough for the layer headers alone");
-    std::vector<uint64_t> windows(layer_count), firsts(layer_count), rows(layer_count);
-    for (uint32_t l = 0; l < layer_count; ++l) {
-        const uint8_t *tag, *reserved;
-        if (!r.take(1, &tag)) return truncated(r, 1);
-        if (!r.take(3, &reserved)) return truncated(r, 3);
-        if (reserved[0] || reserved[1] || reserved[2]) return inconsistent("layer header reserved bytes are not zero");
-        uint64_t window;
-        if (!r.u64(&window)) return truncated(r, 8);
-        if (!r.u64(&firsts[l])) return truncated(r, 8);
-        if (!r.u64(&rows[l])) return truncated(r, 8);
-        if (*tag == 0) {
-            windows[l] = 0;
-        } else if (*tag == 1) {
-            if (window == 0) return inconsistent("windowed layer carries a zero window");
-            windows[l] = window;
-        } else {
-            return inconsistent("layer kind tag " + zu(*tag) + " is not a known kind");
-        }
-    }
-    uint64_t row;
-    if (__builtin_mul_overflow(static_cast<uint64_t>(hkv), static_cast<uint64_t>(hd), &row))
-        return inconsistent("KV row width overflows");
-    std::vector<const uint8_t*> kptr(layer_count), vptr(layer_count);
-    for (uint32_t l = 0; l < layer_count; ++l) {
-        uint64_t floats, nbytes;
-        if (__builtin_mul_overflow(rows[l], row, &floats)) return inconsistent("layer row count overflows the row width");
-        if (__builtin_mul_overflow(floats, static_cast<uint64_t>(4), &nbytes))
-            return inconsistent("float count overflows the byte count");
-        if (!r.take(nbytes, &kptr[l])) return truncated(r, nbytes);
-        if (!r.take(nbytes, &vptr[l])) return truncated(r, nbytes);
-    }
-    uint64_t stored;
-    if (!r.u64(&stored)) return truncated(r, 8);
-    if (r.remaining() != 0) return inconsistent(zu(r.remaining()) + " trailing bytes after the checksum");
-    const uint64_t computed = fnv1a64(bytes, n - 8);
-    if (stored != computed)
-        return b->fail(ITK_ERR_CHECKSUM_MISMATCH, "snapshot: checksum mismatch (stored " + zu(stored) + ", computed " + zu(computed) + ")");
-    // KvSnapshot::validate (snapshot.rs:187-236)
-    if (hkv == 0 || hd == 0) return inconsistent("geometry has a zero KV head count or head dimension");
-    for (uint32_t l = 0; l < layer_count; ++l) {
-        const uint64_t want_rows = windows[l] ? (token_count < windows[l] ? token_count : windows[l]) : token_count;
-        if (firsts[l] != token_count - want_rows)
-            return inconsistent("layer " + zu(l) + ": first stored position is " + zu(firsts[l]) + " but " +
-                                zu(token_count - want_rows) + " follows from token count " + zu(token_count));
-        if (rows[l] != want_rows)
-            return inconsistent("layer " + zu(l) + ": holds " + zu(rows[l]) + " rows but " + zu(want_rows) + " rows were expected");
-    }
+    itk::itkv::Parsed parsed;
+    std::string why;
+    if (int rc = itk::itkv::parse(bytes, n, &parsed, &why)) return b->fail(rc, why);
+    const uint64_t token_count = parsed.token_count;
+    const uint32_t hkv = parsed.kv_heads, hd = parsed.head_dim, layer_count = parsed.layer_count;
+    const std::vector<uint64_t>&windows = parsed.windows, &firsts = parsed.firsts, &rows = parsed.rows;
+    const std::vector<const uint8_t*>&kptr = parsed.kptr, &vptr = parsed.vptr;
+    const uint64_t row = static_cast<uint64_t>(hkv) * hd;
     // restore_checked (snapshot.rs:345-371): geometry, then fingerprint
     bool same = layer_count == b->cfg.n_layers && hkv == b->cfg.kv_heads && hd == b->cfg.head_dim;
     for (uint32_t l = 0; same && l < layer_count; ++l) same = windows[l] == b->window[l];
@@ -1912,7 +1794,7 @@ int itk_snapshot_from_itkv(itk_backend* b, const uint8_t* bytes, size_t n, const
                                                       " layers, " + zu(b->cfg.kv_heads) + " KV heads, head dim " +
                                                       zu(b->cfg.head_dim) + ")");
     if (expected_fingerprint) {
-        const std::string have(reinterpret_cast<const char*>(fp), fp_len);
+        const std::string& have = parsed.fingerprint;
         if (have != expected_fingerprint)
             return b->fail(ITK_ERR_FINGERPRINT_MISMATCH,
                            std::string("fingerprint mismatch: expected ") + expected_fingerprint + ", snapshot has " + have);

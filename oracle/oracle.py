@@ -44,6 +44,13 @@ TRUNCATED = 36
 CHECKSUM_MISMATCH = 37
 GEOMETRY_MISMATCH = 38
 FINGERPRINT_MISMATCH = 39
+EMPTY_PREFIX = 40  # the prefix store's refusals (crates/itak-kv/src/error.rs), raised by oracle/prefix_store.py by name
+TOKEN_COUNT_MISMATCH = 41
+PREFIX_HASH_MISMATCH = 42
+SNAPSHOT_TOKEN_MISMATCH = 43
+ENTRY_TOO_LARGE = 44
+INVALID_CONFIG = 45
+IO = 46
 STEP_FAILED = 64
 
 
