@@ -258,15 +258,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                 mbar_arrive(bar_full + 8 * st);
                 continue;
             }
+            uint32_t sr0 = s0 + row0;
+            if (sr0 >= ring) sr0 -= ring;
+            if (row0 + kTcTile <= span && sr0 + kTcTile <= ring) {
+                // A whole tile inside the split and inside the ring (all but a sequence's last tile and a sliding
+                // layer's wrap): this thread's 64 copies differ by constants only - rows rg, rg + 2, ... are 512 bytes
+                // apart in the cache, and their swizzled places repeat every four rows, 1024 bytes on - so that one
+                // loader warp issues a tile in a few hundred instructions instead of a thousand.
+                const __half* g = col + static_cast<size_t>(sr0 + rg) * D;
+                const uint32_t sb = dst + soff_c;
+                const uint32_t o0 = panel_off(rg, cc), o1 = panel_off(rg + 2, cc), o2 = panel_off(rg + 4, cc),
+                               o3 = panel_off(rg + 6, cc);
+#pragma unroll 4
+                for (int i = 0; i < kTcTile / 8; ++i) {
+                    cp_async16(sb + 1024 * i + o0, g + (8 * i) * D, 16u);
+                    cp_async16(sb + 1024 * i + o1, g + (8 * i + 2) * D, 16u);
+                    cp_async16(sb + 1024 * i + o2, g + (8 * i + 4) * D, 16u);
+                    cp_async16(sb + 1024 * i + o3, g + (8 * i + 6) * D, 16u);
+                }
+            } else {
 #pragma unroll 8
-            for (int i = 0; i < kTcTile / 2; ++i) {
-                const uint32_t row = rg + 2 * i;
-                const uint32_t kr = row0 + row;
-                const bool valid = kr < span;
-                uint32_t srow = s0 + kr;
-                if (srow >= ring) srow -= ring;
-                cp_async16(dst + soff_c + panel_off(row, cc), col + static_cast<size_t>(valid ? srow : 0u) * D,
-                           valid ? 16u : 0u);
+                for (int i = 0; i < kTcTile / 2; ++i) {
+                    const uint32_t row = rg + 2 * i;
+                    const uint32_t kr = row0 + row;
+                    const bool valid = kr < span;
+                    uint32_t srow = s0 + kr;
+                    if (srow >= ring) srow -= ring;
+                    cp_async16(dst + soff_c + panel_off(row, cc), col + static_cast<size_t>(valid ? srow : 0u) * D,
+                               valid ? 16u : 0u);
+                }
             }
             // The stage's full barrier receives this thread's arrival when the copies above have landed; nobody waits.
             cp_async_arrive_noinc(bar_full + 8 * st);
