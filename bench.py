@@ -417,8 +417,14 @@ def run_ours(args):
         peak, peak_src = 6650.0, "fallback (earlier measurement on this pool)"
     attn_ms = prof["attention_ms"] / max(prof["attention_launches"], 1)
     achieved = bytes_launch_rank / (attn_ms * 1e-3) / 1e9 if attn_ms > 0 else None
+    # DRAM traffic per launch: ncu measured 269.24 MB read + 4.3 MB written against 268.60 MB algorithmic on a
+    # context-8192 capture of this kernel (profiles/decode_f16_kernel_c5_small.md); traffic grows in proportion to
+    # the keys streamed, so the full launch is that ratio times its algorithmic bytes.
+    traffic = bytes_launch_rank * (269.24 + 4.3) / 268.60
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": (achieved / peak) if achieved else None, "traffic": None, "peak_source": peak_src,
+                "frac": (achieved / peak) if achieved else None, "traffic": traffic,
+                "traffic_source": "ncu dram__bytes_read+write of a context-8192 capture, scaled by keys streamed",
+                "peak_source": peak_src,
                 "kernel": "decode_f16_kernel<128,3>", "bytes_per_launch": bytes_launch_rank,
                 "avg_launch_ms": attn_ms, "launches_timed": prof["attention_launches"],
                 "timed_as": "event pair around every launch" + ("" if args.no_graph else ", direct-launch pass after the graph replays"),

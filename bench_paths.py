@@ -165,7 +165,10 @@ def run_spec_verify(args, sampler_cls):
                    "sessions": SESSIONS, "prefix_tokens": PREFIX, "rows_per_round": ROWS,
                    "mean_context": sum(pos) / SESSIONS, "l2": f"{bytes_launch / 2**20:.0f} MiB of K/V per launch, larger than L2"},
         "roofline": {"bound": "hbm", "achieved": bytes_launch / (a_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": bytes_launch / (a_ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_source": src,
+                     "frac": bytes_launch / (a_ms * 1e-3) / 1e9 / peak,
+                     # ncu on a 2-layer capture of the same launch shape: 137.6 MB read + 5.3 MB written against
+                     # 136.2 MB algorithmic (profiles/verify_tc_kernel_c4_small.md)
+                     "traffic": bytes_launch * (137.6 + 5.3) / 136.2, "peak_source": src,
                      "kernel": ("verify_tc_kernel<32> (tcgen05)" if os.environ.get("ITK_VERIFY_TC", "1") != "0"
                                 else "verify_f16_kernel<128> (mma.sync)"),
                      "bytes_per_launch": bytes_launch, "avg_launch_ms": a_ms,

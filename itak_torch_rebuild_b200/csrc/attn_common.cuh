@@ -158,8 +158,7 @@ __device__ __forceinline__ void finish_weights(const float* all_ml, uint32_t n_p
 template <int THREADS, int MAXP>
 __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t n_parts,
                                             uint32_t part, uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
-                                            const float* fm, const float* fl, int* s_flag, float* wscratch,
-                                            unsigned char* stage = nullptr, uint32_t stage_bytes = 0) {
+                                            const float* fm, const float* fl, int* s_flag, float* wscratch) {
     const uint32_t tid = threadIdx.x;
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
     const size_t out_off = (static_cast<size_t>(unit) * p.q_heads + head0) * D;  // element offset of the cell's rows
@@ -206,49 +205,6 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
     const float4* src4 = reinterpret_cast<const float4*>(all_o);
     uint32_t c0 = tid, c1 = tid + THREADS;
     bool one = vec && c0 < cols, two = vec && c1 < cols;
-    if (stage != nullptr && vec && cols <= 2 * THREADS && stage_bytes >= 2 * cols * 16) {
-        // Staged path (the caller's shared memory is idle): the partial outputs of as many parts as fit are copied
-        // asynchronously into shared memory, all of them in flight at once and without a register per load, while
-        // the weights are worked out; a cell shared by a few dozen CTAs is merged in one or two round trips.
-        const uint32_t per_round = stage_bytes / (cols * 16);
-        const uint32_t stage_addr = smem_u32(stage);
-        const float4* stage4 = reinterpret_cast<const float4*>(stage);
-        const uint32_t h0 = one ? (c0 * 4) / D : 0u, h1 = two ? (c1 * 4) / D : h0;
-        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-        for (uint32_t s0 = 0; s0 < n_parts; s0 += per_round) {
-            const uint32_t cnt = min(per_round, n_parts - s0);
-            for (uint32_t idx = tid; idx < cnt * cols; idx += THREADS) {
-                const uint32_t sp = idx / cols, c = idx % cols;
-                cp_async16(stage_addr + idx * 16, src4 + (s0 + sp) * pstride + c, 16u);
-            }
-            cp_async_commit();
-            if (s0 == 0) {
-                finish_weights<THREADS, MAXP>(all_ml, n_parts, nh, w_m, w_l, inv_l);
-                ITK_TRACE(p, 11);
-            }
-            cp_async_wait<0>();
-            __syncthreads();
-            for (uint32_t sp = 0; sp < cnt; ++sp) {
-                const float w0 = w_m[(s0 + sp) * kHeadsPerCta + h0], w1 = w_m[(s0 + sp) * kHeadsPerCta + h1];
-                if (one) {
-                    const float4 v = stage4[sp * cols + c0];
-                    a0.x += w0 * v.x; a0.y += w0 * v.y; a0.z += w0 * v.z; a0.w += w0 * v.w;
-                }
-                if (two) {
-                    const float4 v = stage4[sp * cols + c1];
-                    a1.x += w1 * v.x; a1.y += w1 * v.y; a1.z += w1 * v.z; a1.w += w1 * v.w;
-                }
-            }
-            if (s0 + per_round < n_parts) __syncthreads();  // the next round overwrites the staging area
-        }
-        ITK_TRACE(p, 12);
-        const float i0 = inv_l[h0], i1 = inv_l[h1];
-        if (one) store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
-        if (two) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
-        signal_cell_delivered(p);
-        if (tid == 0) p.tickets[cell] = 0u;
-        return;
-    }
     float4 v0[kBatch], v1[kBatch];
     auto load_batch = [&](uint32_t s) {
 #pragma unroll

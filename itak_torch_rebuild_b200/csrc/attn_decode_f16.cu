@@ -239,13 +239,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     };
 
     uint32_t issued = 0;
-    bool waited = p.pdl != 2;
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (!waited && static_cast<uint32_t>(s) >= (p.early_tiles & 0xffu)) {
-            pdl_wait();
-            waited = true;
-        }
         if (issued < ntiles) {
             load_tile(lc, issued % STAGES);
             advance(lc);
@@ -257,7 +252,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     // The cache rows streamed above do not depend on the previous kernel; the queries, the step's new row
     // and the merge scratch do.
     ITK_TRACE(p, 2);
-    if (!waited) pdl_wait();
+    if (p.pdl == 2) pdl_wait();
     ITK_TRACE(p, 3);
 
     // A layer's inputs exist only once every rank's heads of the previous layer have been gathered: check that the
@@ -518,10 +513,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 n_parts = last - first + 1;
                 part = blockIdx.x - first;
             }
-            // (at the end of the run the idle pipeline doubles as the merge's staging area)
             finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm, fl, flag,
-                                                         wscratch, (p.early_tiles & 0x100u) && i + 1 == ntiles ? smem : nullptr,
-                                                         static_cast<uint32_t>(decode_pipe_bytes<D, STAGES>()));
+                                                         wscratch);
             fresh = true;
         }
         advance(cc);

@@ -172,6 +172,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t ntiles = (span + kTcTile - 1) / kTcTile;
 
     if (tid == 0) TC_TRACE(p, 256);
+    // The query rows are requested first of all (each softmax warp a quarter of the CTA's PC distinct rows, lane l
+    // the 16-byte chunk l of a row), so that their latency runs underneath the set-up below instead of behind the
+    // opening burst of K/V tile loads.
+    float4 q_ld[PC / 4];
+    if (warp < kTcMmaWarp) {
+#pragma unroll
+        for (int rr = 0; rr < PC / 4; ++rr) {
+            const uint32_t spair = pc * PC + warp * (PC / 4) + rr;
+            q_ld[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (spair < n_pairs)
+                q_ld[rr] = __ldg(reinterpret_cast<const float4*>(
+                                     p.q + ((static_cast<size_t>(seq) * p.rows + spair / nh) * p.q_heads + head0 + spair % nh) *
+                                               kTcD) + lane);
+        }
+    }
     if (tid == 0) {
         for (int s = 0; s < kTcStagesK; ++s) {
             tc::mbar_init(bar_full_k + 8 * s, kTcLoaderThreads);
@@ -227,11 +242,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             // Only the first K tile is requested before the query rows have arrived: a load issued together with
             // the CTAs' opening burst of hundreds of KiB each waits microseconds for its turn, and the first scores
             // need the queries.  (The last V stage also doubles as the staging area of the query rows.)
+            const uint32_t row0 = tile * kTcTile;
+            const bool has_new = new_src != nullptr && static_cast<int64_t>(row0) + kTcTile > new_rel;
+            // The first few of the block's own rows that fall to this thread are requested before it waits for the
+            // stage: they are plain (synchronous) loads, and one round trip each would otherwise sit on the path of
+            // the block's last tile.
+            constexpr int kPre = 4;
+            float4 pre[kPre][2];
+            int pre_i0 = 0;
+            if (has_new) {
+                const int64_t first = new_rel - static_cast<int64_t>(row0) - rg;  // row index (rg + 2i) of the first new row
+                pre_i0 = first > 0 ? static_cast<int>((first + 1) / 2) : 0;
+#pragma unroll
+                for (int j = 0; j < kPre; ++j) {
+                    const uint32_t kr = row0 + rg + 2 * (pre_i0 + j);
+                    pre[j][0] = pre[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (pre_i0 + j < kTcTile / 2 && kr < span) {
+                        const float* src = new_src + static_cast<size_t>(kr - new_rel) * p.layer.kv_heads * D;
+                        pre[j][0] = *reinterpret_cast<const float4*>(src);
+                        pre[j][1] = *reinterpret_cast<const float4*>(src + 4);
+                    }
+                }
+            }
             if (tile == (is_v ? 0u : 1u) && !wait_or_abort(bar_go, 0u, abort_flag)) break;
             if (tile >= nst && !wait_or_abort(bar_empty + 8 * st, (tile / nst - 1) & 1u, abort_flag)) break;
             const uint32_t dst = buf + st * kStageBytes;
-            const uint32_t row0 = tile * kTcTile;
-            if (new_src != nullptr && static_cast<int64_t>(row0) + kTcTile > new_rel) {
+            if (has_new) {
                 // The tile holds rows of the block itself, which no append launch has stored: they are converted
                 // here from the caller's f32 rows (the append kernel's conversion), dropped straight into the stage,
                 // and stored to the cache by the one CTA of this (sequence, KV head) that is in charge of that.
@@ -243,8 +279,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                     if (srow >= ring) srow -= ring;
                     if (valid && static_cast<int64_t>(kr) >= new_rel) {
                         const float* src = new_src + static_cast<size_t>(kr - new_rel) * p.layer.kv_heads * D;
-                        const uint4 packed = pack8(*reinterpret_cast<const float4*>(src),
-                                                   *reinterpret_cast<const float4*>(src + 4));
+                        const int j = i - pre_i0;
+                        float4 f0, f1;
+                        if (j >= 0 && j < kPre) {
+                            // (selected by constant index so that `pre` stays in registers)
+                            f0 = j == 0 ? pre[0][0] : j == 1 ? pre[1][0] : j == 2 ? pre[2][0] : pre[3][0];
+                            f1 = j == 0 ? pre[0][1] : j == 1 ? pre[1][1] : j == 2 ? pre[2][1] : pre[3][1];
+                        } else {
+                            f0 = *reinterpret_cast<const float4*>(src);
+                            f1 = *reinterpret_cast<const float4*>(src + 4);
+                        }
+                        const uint4 packed = pack8(f0, f1);
                         *reinterpret_cast<uint4*>(smem + (dst - kbuf) + soff_c + panel_off(row, cc)) = packed;
                         if (stores_new)
                             *reinterpret_cast<uint4*>(const_cast<__half*>(col) + static_cast<size_t>(srow) * D) = packed;
@@ -379,22 +424,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             // warp a quarter of the CTA's PC distinct rows, into a staging area in shared memory (chunk l of row i
             // at position l ^ (i & 31): conflict-free both ways).  Then every thread reads the row of its pair.
             unsigned char* stage_q = smem + (vbuf - kbuf) + (kTcStagesV - 1) * kStageBytes;
-            {
-                float4 ld[PC / 4];
 #pragma unroll
-                for (int rr = 0; rr < PC / 4; ++rr) {
-                    const uint32_t srow = warp * (PC / 4) + rr, spair = pc * PC + srow;
-                    ld[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (spair < n_pairs)
-                        ld[rr] = __ldg(reinterpret_cast<const float4*>(
-                                           p.q + ((static_cast<size_t>(seq) * p.rows + spair / nh) * p.q_heads + head0 +
-                                                  spair % nh) * D) + lane);
-                }
-#pragma unroll
-                for (int rr = 0; rr < PC / 4; ++rr) {
-                    const uint32_t srow = warp * (PC / 4) + rr;
-                    *reinterpret_cast<float4*>(stage_q + srow * 512 + ((lane ^ (srow & 31u)) << 4)) = ld[rr];
-                }
+            for (int rr = 0; rr < PC / 4; ++rr) {
+                const uint32_t srow = warp * (PC / 4) + rr;
+                *reinterpret_cast<float4*>(stage_q + srow * 512 + ((lane ^ (srow & 31u)) << 4)) = q_ld[rr];
             }
             softmax_sync();
             // (a rolled loop: one-time code is kept small)

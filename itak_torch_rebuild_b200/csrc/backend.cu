@@ -118,7 +118,6 @@ struct itk_backend {
     bool gth_wait = true;  // ITK_GATHER_WAIT=0: do not check the peers' previous launch at kernel start
     int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
     bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
-    uint32_t early_tiles = 8; // ITK_DECODE_EARLY_TILES: tiles each warp pipeline requests before the dependency wait (up to its depth)
     // attention preparation (per-head RMSNorm + rotary rotation), configured per layer
     struct LayerPrep {
         bool set = false;
@@ -629,7 +628,6 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
     if (const char* env = std::getenv("ITK_GATHER_WAIT")) b->gth_wait = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_DECODE_EARLY_TILES")) b->early_tiles = static_cast<uint32_t>(std::atoi(env));
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_VERIFY_TC")) b->verify_tc = std::atoi(env) != 0;
@@ -861,7 +859,6 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     }
     // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
     // the same layer) the kernel waits first.
-    p.early_tiles = b->early_tiles;
     p.pdl = !b->use_pdl ? 0u : ((b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer) ? 2u : 1u);
     ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
              "resident decode launch");

@@ -91,7 +91,6 @@ struct AttnLaunch {
     uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
-    uint32_t early_tiles;    // decode kernel with pdl == 2: tiles per warp pipeline requested before the wait
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
