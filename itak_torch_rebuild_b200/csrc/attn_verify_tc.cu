@@ -271,32 +271,62 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                 // The tile holds rows of the block itself, which no append launch has stored: they are converted
                 // here from the caller's f32 rows (the append kernel's conversion), dropped straight into the stage,
                 // and stored to the cache by the one CTA of this (sequence, KV head) that is in charge of that.
-                for (int i = 0; i < kTcTile / 2; ++i) {
-                    const uint32_t row = rg + 2 * i;
-                    const uint32_t kr = row0 + row;
-                    const bool valid = kr < span;
-                    uint32_t srow = s0 + kr;
-                    if (srow >= ring) srow -= ring;
-                    if (valid && static_cast<int64_t>(kr) >= new_rel) {
-                        const float* src = new_src + static_cast<size_t>(kr - new_rel) * p.layer.kv_heads * D;
-                        const int j = i - pre_i0;
-                        float4 f0, f1;
-                        if (j >= 0 && j < kPre) {
-                            // (selected by constant index so that `pre` stays in registers)
-                            f0 = j == 0 ? pre[0][0] : j == 1 ? pre[1][0] : j == 2 ? pre[2][0] : pre[3][0];
-                            f1 = j == 0 ? pre[0][1] : j == 1 ? pre[1][1] : j == 2 ? pre[2][1] : pre[3][1];
-                        } else {
-                            f0 = *reinterpret_cast<const float4*>(src);
-                            f1 = *reinterpret_cast<const float4*>(src + 4);
-                        }
-                        const uint4 packed = pack8(f0, f1);
-                        *reinterpret_cast<uint4*>(smem + (dst - kbuf) + soff_c + panel_off(row, cc)) = packed;
-                        if (stores_new)
-                            *reinterpret_cast<uint4*>(const_cast<__half*>(col) + static_cast<size_t>(srow) * D) = packed;
-                    } else {
+                // This thread's rows rg + 2i of the tile: i < n_old come from the cache, n_old <= i < n_valid are the
+                // block's own, the rest lie past the split and are zero-filled.
+                const int n_valid = span > row0 + rg ? static_cast<int>(min(static_cast<uint32_t>(kTcTile / 2), (span - row0 - rg + 1) / 2)) : 0;
+                const int n_old = min(pre_i0, n_valid);
+                uint32_t nr0 = s0 + row0;
+                if (nr0 >= ring) nr0 -= ring;
+                if (nr0 + kTcTile <= ring) {
+                    // no ring wrap inside the tile: constant offsets, as in the whole-tile path below
+                    const __half* g = col + static_cast<size_t>(nr0 + rg) * D;
+                    const uint32_t sb = dst + soff_c;
+                    const uint32_t o0 = panel_off(rg, cc), o1 = panel_off(rg + 2, cc), o2 = panel_off(rg + 4, cc),
+                                   o3 = panel_off(rg + 6, cc);
+                    auto put = [&](int i, uint32_t sa, const __half* ga) {
+                        if (i < n_old)
+                            cp_async16(sa, ga, 16u);
+                        else if (i >= n_valid)
+                            cp_async16(sa, g, 0u);  // 16 zero bytes, nothing read
+                    };
+#pragma unroll 4
+                    for (int i = 0; i < kTcTile / 8; ++i) {
+                        put(4 * i, sb + 1024 * i + o0, g + (8 * i) * D);
+                        put(4 * i + 1, sb + 1024 * i + o1, g + (8 * i + 2) * D);
+                        put(4 * i + 2, sb + 1024 * i + o2, g + (8 * i + 4) * D);
+                        put(4 * i + 3, sb + 1024 * i + o3, g + (8 * i + 6) * D);
+                    }
+                } else {
+                    for (int i = 0; i < kTcTile / 2; ++i) {
+                        if (i >= n_old && i < n_valid) continue;
+                        const uint32_t row = rg + 2 * i;
+                        uint32_t srow = s0 + row0 + row;
+                        if (srow >= ring) srow -= ring;
+                        const bool valid = i < n_old;
                         cp_async16(dst + soff_c + panel_off(row, cc), col + static_cast<size_t>(valid ? srow : 0u) * D,
                                    valid ? 16u : 0u);
                     }
+                }
+                for (int i = pre_i0; i < n_valid; ++i) {
+                    const uint32_t row = rg + 2 * i;
+                    const uint32_t kr = row0 + row;
+                    uint32_t srow = s0 + kr;
+                    if (srow >= ring) srow -= ring;
+                    const int j = i - pre_i0;
+                    float4 f0, f1;
+                    if (j < kPre) {
+                        // (selected by constant index so that `pre` stays in registers)
+                        f0 = j == 0 ? pre[0][0] : j == 1 ? pre[1][0] : j == 2 ? pre[2][0] : pre[3][0];
+                        f1 = j == 0 ? pre[0][1] : j == 1 ? pre[1][1] : j == 2 ? pre[2][1] : pre[3][1];
+                    } else {
+                        const float* src = new_src + static_cast<size_t>(kr - new_rel) * p.layer.kv_heads * D;
+                        f0 = *reinterpret_cast<const float4*>(src);
+                        f1 = *reinterpret_cast<const float4*>(src + 4);
+                    }
+                    const uint4 packed = pack8(f0, f1);
+                    *reinterpret_cast<uint4*>(smem + (dst - kbuf) + soff_c + panel_off(row, cc)) = packed;
+                    if (stores_new)
+                        *reinterpret_cast<uint4*>(const_cast<__half*>(col) + static_cast<size_t>(srow) * D) = packed;
                 }
                 cp_async_wait_all();
                 tc::fence_proxy_async();  // plain stores into the stage: visible to the tensor core before the arrival
