@@ -87,6 +87,7 @@ __device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p) {
                      : "memory");
 }
 
+constexpr uint32_t kFusedSumMinParts = 13;  // cells shared by more parts than one register batch take the fused sum
 constexpr int kMaxSplits = 256;  // upper bound on the partials merged for one cell (sizes the merge scratch)
 
 // The merge's per-part weights: reads the (max, sum) pairs of every part of a cell (all requested together), then
@@ -178,6 +179,29 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
         pml[2 * tid] = fm[tid];
         pml[2 * tid + 1] = fl[tid];
     }
+    // A cell shared by many CTAs is not merged by reading every part back: each part also adds its output, scaled
+    // by 2^max of the part, into one accumulator per cell with reductions performed in L2, and the last arrival
+    // only reads that sum.  Sums of terms scaled by their own maxima are as good as sums scaled by the common
+    // maximum while every factor stays far inside the f32 range; a part whose maximum lies outside
+    // [-kAccRange, kAccRange] (log2 domain) raises the cell's flag instead and the merge below takes the exact path
+    // over the stored parts.  The order of the additions varies from launch to launch, so results on this path agree
+    // to rounding, not bit for bit.
+    constexpr float kAccRange = 60.f;
+    const bool fused_sum = p.acc_o != nullptr && n_parts > kFusedSumMinParts && (D & 3u) == 0 && nh * D / 4 <= 2 * THREADS;
+    if (fused_sum) {
+        bool in_range = true;
+        for (uint32_t h = 0; h < nh; ++h) in_range = in_range && (fm[h] == -INFINITY || fabsf(fm[h]) <= kAccRange);
+        if (in_range) {
+            float* ao = p.acc_o + cell * (kHeadsPerCta * D);
+            for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
+                const float m = fm[idx / D];
+                if (m != -INFINITY) atomicAdd(ao + idx, fo[idx] * fast_exp2(m));
+            }
+            if (tid < nh && fm[tid] != -INFINITY) atomicAdd(p.acc_l + cell * kHeadsPerCta + tid, fl[tid] * fast_exp2(fm[tid]));
+        } else if (tid == 0) {
+            atomicOr(p.acc_flag + cell, 1u);
+        }
+    }
     __threadfence();
     __syncthreads();
     ITK_TRACE(p, 8);
@@ -190,6 +214,38 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
     if (*s_flag == 0) return;
     ITK_TRACE(p, 6);  // this CTA drew the last ticket of a cell and merges it
     __threadfence();
+    if (fused_sum) {
+        float* ao = p.acc_o + cell * (kHeadsPerCta * D);
+        float* al = p.acc_l + cell * kHeadsPerCta;
+        const unsigned int slow = __ldcg(p.acc_flag + cell);
+        {
+            const uint32_t cols = nh * D / 4, c0 = tid, c1 = tid + THREADS;
+            float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+            float l0 = 1.f, l1 = 1.f;
+            if (c0 < cols) {
+                a0 = __ldcg(reinterpret_cast<const float4*>(ao) + c0);
+                l0 = __ldcg(al + (c0 * 4) / D);
+            }
+            if (c1 < cols) {
+                a1 = __ldcg(reinterpret_cast<const float4*>(ao) + c1);
+                l1 = __ldcg(al + (c1 * 4) / D);
+            }
+            __syncthreads();  // every thread holds its share: the accumulators can be cleared for the next launch
+            const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c0 < cols) reinterpret_cast<float4*>(ao)[c0] = zero;
+            if (c1 < cols) reinterpret_cast<float4*>(ao)[c1] = zero;
+            if (tid < kHeadsPerCta) al[tid] = 0.f;
+            if (tid == 0) p.acc_flag[cell] = 0u;
+            if (slow == 0u) {
+                const float i0 = 1.f / l0, i1 = 1.f / l1;
+                if (c0 < cols) store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
+                if (c1 < cols) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
+                signal_cell_delivered(p);
+                if (tid == 0) p.tickets[cell] = 0u;
+                return;
+            }
+        }
+    }
     const float* all_o = p.part_o + cell * p.splits * (kHeadsPerCta * D);
     const float* all_ml = p.part_ml + cell * p.splits * (kHeadsPerCta * 2);
     float* w_m = wscratch;                        // [splits][8] maxima, then weights

@@ -86,6 +86,10 @@ struct itk_backend {
     float* part_o = nullptr;
     float* part_ml = nullptr;
     unsigned int* tickets = nullptr;
+    float* acc_o = nullptr;  // fused-sum accumulators of the resident decode loop: [ticket_cells][8][head_dim], [..][8]
+    float* acc_l = nullptr;
+    unsigned int* acc_flag = nullptr;
+    bool fused_sum = true;   // ITK_DECODE_FUSED_SUM=0: cells shared by many CTAs are merged from the stored parts
     size_t ticket_cells = 0;
     float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_out = nullptr;
     size_t stage_rows = 0;
@@ -602,6 +606,18 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     e = cudaMalloc(&b->tickets, b->ticket_cells * sizeof(unsigned int));
     if (e != cudaSuccess) return cuda_refuse(e, "ticket allocation");
     cudaMemsetAsync(b->tickets, 0, b->ticket_cells * sizeof(unsigned int), b->stream);
+    {
+        const size_t ao = b->ticket_cells * itk::kHeadsPerCta * cfg->head_dim * sizeof(float);
+        const size_t al = b->ticket_cells * itk::kHeadsPerCta * sizeof(float);
+        if (cudaMalloc(&b->acc_o, ao) == cudaSuccess && cudaMalloc(&b->acc_l, al) == cudaSuccess &&
+            cudaMalloc(&b->acc_flag, b->ticket_cells * sizeof(unsigned int)) == cudaSuccess) {
+            cudaMemsetAsync(b->acc_o, 0, ao, b->stream);
+            cudaMemsetAsync(b->acc_l, 0, al, b->stream);
+            cudaMemsetAsync(b->acc_flag, 0, b->ticket_cells * sizeof(unsigned int), b->stream);
+        } else {
+            return cuda_refuse(cudaErrorMemoryAllocation, "fused-sum accumulator allocation");
+        }
+    }
     e = cudaMalloc(&b->part_o, kPartCellSplits * itk::kHeadsPerCta * cfg->head_dim * sizeof(float));
     if (e != cudaSuccess) return cuda_refuse(e, "partial-output scratch allocation");
     e = cudaMalloc(&b->part_ml, kPartCellSplits * itk::kHeadsPerCta * 2 * sizeof(float));
@@ -628,6 +644,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
     if (const char* env = std::getenv("ITK_GATHER_WAIT")) b->gth_wait = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
+    if (const char* env = std::getenv("ITK_DECODE_FUSED_SUM")) b->fused_sum = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
     if (const char* env = std::getenv("ITK_VERIFY_TC")) b->verify_tc = std::atoi(env) != 0;
@@ -642,6 +659,9 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->k_slab);
     cudaFree(b->v_slab);
     cudaFree(b->tickets);
+    cudaFree(b->acc_o);
+    cudaFree(b->acc_l);
+    cudaFree(b->acc_flag);
     for (auto& lp : b->prep) {
         cudaFree(lp.q_w);
         cudaFree(lp.k_w);
@@ -833,6 +853,11 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     p.k_new = d_k;
     p.v_new = d_v;
     p.seq_dev = b->d_states;
+    if (b->fused_sum) {
+        p.acc_o = b->acc_o;
+        p.acc_l = b->acc_l;
+        p.acc_flag = b->acc_flag;
+    }
 #ifdef ITK_DECODE_TRACE
     p.trace = g_trace ? g_trace + static_cast<size_t>(layer % 64) * 512 * 16 : nullptr;
 #endif

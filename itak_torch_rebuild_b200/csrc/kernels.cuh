@@ -77,6 +77,10 @@ struct AttnLaunch {
     float* part_o;           // [unit][hy][split][8][D] unnormalised partial outputs
     float* part_ml;          // [unit][hy][split][8][2] running max (log2 domain) and sum
     unsigned int* tickets;   // [unit][hy] arrival counters, zero between launches
+    float* acc_o;            // decode kernel, optional: [unit][hy][8][D] sums of the parts' outputs, each scaled by
+    float* acc_l;            // 2^max of its part, and [unit][hy][8] of their weight sums, added to with reductions
+    unsigned int* acc_flag;  // in L2; [unit][hy] raised when a part's maximum is outside the range that makes such
+                             // sums safe, which sends the cell's merge down the exact path.  All zero between launches.
     uint32_t q_heads;
     uint32_t group;          // q_heads / kv_heads
     uint32_t gchunks;        // ceil(group / 8): head chunks per kv head

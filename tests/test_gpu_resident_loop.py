@@ -6,6 +6,7 @@ import pytest
 from itak_torch_rebuild_b200 import CudaCompute, CudaComputeError, KvDtype, _lib
 
 from kvparity import assert_view_equal, attention_error, make_pair, stored
+from oracle import oracle as orc
 
 pytestmark = pytest.mark.gpu
 
@@ -120,3 +121,46 @@ def test_resident_loop_refusals():
     with pytest.raises(CudaComputeError) as e:
         f32.resident_begin([0], 1)
     assert e.value.code == _lib.ERR_INVALID_ARGUMENT
+
+
+@pytest.mark.parametrize("q_scale", [1.0, 40.0])
+def test_resident_loop_cells_shared_by_many_ctas(q_scale):
+    """A KV-head shard's shape - few (sequence, head) cells, each shared by dozens of CTAs - takes the cell-aligned plan
+    and sums the parts with reductions in L2 instead of merging them one by one; scores beyond the range that keeps
+    such sums safe (q_scale 40: maxima of several hundred in the log2 domain) send the cell down the exact merge.
+    Both must match the oracle on every step and layer (the accumulators are cleared between launches)."""
+    import torch
+
+    layer_window, hq, hkv, d = [0, 0], 8, 1, 128
+    lens, steps = [2500, 2449], 3
+    layers, n = len(layer_window), len(lens)
+    a, refs = build(layer_window, hq, hkv, d, lens, 2600, seed=21)
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(4)
+    q = (q_scale * rng.standard_normal((steps, layers, n, hq * d))).astype(np.float32)
+    k = rng.standard_normal((steps, layers, n, hkv * d)).astype(np.float32)
+    v = rng.standard_normal((steps, layers, n, hkv * d)).astype(np.float32)
+    q_d = torch.empty((layers, n, hq * d), device=dev)
+    k_d = torch.empty((layers, n, hkv * d), device=dev)
+    v_d = torch.empty((layers, n, hkv * d), device=dev)
+    out_d = torch.empty((layers, n, hq * d), device=dev)
+    slots = list(range(n))
+    a.resident_begin(slots, steps)
+    for s in range(steps):
+        q_d.copy_(torch.from_numpy(q[s]))
+        k_d.copy_(torch.from_numpy(k[s]))
+        v_d.copy_(torch.from_numpy(v[s]))
+        torch.cuda.synchronize()
+        for layer in range(layers):
+            a.resident_layer(layer, q_d[layer].data_ptr(), k_d[layer].data_ptr(), v_d[layer].data_ptr(),
+                             out_d[layer].data_ptr())
+        a.resident_advance()
+        a.synchronize()
+        got = out_d.cpu().numpy()
+        for slot in range(n):
+            for layer in range(layers):
+                refs[slot].append(layer, stored(k[s, layer, slot], KvDtype.F16), stored(v[s, layer, slot], KvDtype.F16),
+                                  lens[slot] + s)
+                want = orc.gqa_attention(q[s, layer, slot], 1, hq, [lens[slot] + s], refs[slot].view(layer))
+                assert attention_error(got[layer, slot], want, hq, d) <= 2e-3, f"step {s} layer {layer} slot {slot}"
+    a.resident_end(steps)
