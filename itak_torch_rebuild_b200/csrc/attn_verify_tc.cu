@@ -33,10 +33,12 @@
 // The accumulator is rescaled in tensor memory only when a row's maximum grows by more than 2^8 (the stale
 // maximum is used consistently for weights and sum until then, so the result is exact).
 //
-// The CTA is warp-specialised (7 warps):
+// The CTA is warp-specialised (8 warps):
 //   warps 0-3  softmax: thread i owns tensor-memory lane i;
-//   warp  4    issues every MMA (one lane) - issuing blocks while the tensor queue is full, so it must not
+//   warp  4    issues the score MMAs (one lane) - issuing blocks while the tensor queue is full, so it must not
 //              sit in a warp that also has softmax work - and owns the tensor-memory allocation;
+//   warp  7    issues the P * V MMAs (one lane): with one issuer for both kinds, its waits and fences between a
+//              tile's value product and the next tile's scores left the tensor core idle a quarter of the time;
 //   warp 5 streams K tiles, warp 6 V tiles, with 16-byte cp.async (zero-filled past the split's range)
 //              into rings of three (K) and four (V) 32 KiB stages - a K stage is free again as soon as its
 //              scores are complete, a V stage only after P * V; each copy batch reports its own completion to
@@ -67,8 +69,9 @@ namespace {
 
 constexpr int kTcSoftmaxThreads = 128;
 constexpr int kTcLoaderThreads = 32;  // per stream (K, V)
-constexpr int kTcThreads = kTcSoftmaxThreads + 32 + 2 * kTcLoaderThreads;
-constexpr int kTcMmaWarp = 4;
+constexpr int kTcThreads = kTcSoftmaxThreads + 32 + 2 * kTcLoaderThreads + 32;
+constexpr int kTcMmaWarp = 4;  // issues the score MMAs and owns the tensor-memory allocation
+constexpr int kTcPvWarp = 7;   // issues the P * V MMAs
 constexpr int kTcTile = 128;   // keys per tile
 constexpr int kTcStagesK = 3;  // K ring depth
 constexpr int kTcStagesV = 4;  // V ring depth
@@ -216,7 +219,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     tc::fence_after_sync();
     const uint32_t tmem = *slot_ptr;
 
-    if (warp > kTcMmaWarp) {
+    if (warp > kTcMmaWarp && warp < kTcPvWarp) {
         // ---------------- loaders: warp 5 streams K, warp 6 streams V; thread lt copies 16-byte chunk c of rows
         // rg, rg + 2, ... of every tile
         const bool is_v = warp > kTcMmaWarp + 1;
@@ -369,21 +372,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         }
         cp_async_wait_all();
     } else if (warp == kTcMmaWarp) {
-        // ---------------- MMA issuer: one lane issues everything (tcgen05.commit tracks that thread's MMAs)
+        // ---------------- score MMAs: one lane issues S = [q_hi | q_lo] * [K | K]^T for every tile
+        // (tcgen05.commit tracks the issuing thread's MMAs).  The next tile's scores run underneath this tile's
+        // softmax, as soon as every softmax thread has taken this tile's scores into registers.
         if (lane == 0 && ntiles > 0) {
             constexpr uint32_t kIdescS = tc::instr_desc_f16(128, kTcTile, false);
-            constexpr uint32_t kIdescO = tc::instr_desc_f16(128, D, true);
-            auto issue_qk = [&](uint32_t tile) {  // S = [q_hi | q_lo] * [K | K]^T, 16 halfs of the contraction per MMA
-                const uint32_t kst = kbuf + (tile % kTcStagesK) * kStageBytes;
+            if (wait_or_abort(bar_q, 0u, abort_flag)) {
+                for (uint32_t tile = 0; tile < ntiles; ++tile) {
+                    if (*abort_flag != 0) break;
+                    if (!wait_or_abort(bar_full_k + 8 * (tile % kTcStagesK), (tile / kTcStagesK) & 1u, abort_flag)) break;
+                    if (tile > 0 && !wait_or_abort(bar_sfree, (tile - 1) & 1u, abort_flag)) break;
+                    tc::fence_proxy_async();  // the tile was written through the generic proxy (cp.async)
+                    tc::fence_after_sync();
+                    TC_TRACE(p, tile * 8 + 0);
+                    const uint32_t kst = kbuf + (tile % kTcStagesK) * kStageBytes;
 #pragma unroll
-                for (int ks = 0; ks < 16; ++ks)
-                    tc::mma_f16_ts(tmem + kTmemS, tmem + kTmemQ + 8 * ks,
-                                   tc::smem_desc(kst + ((ks % 8) / 4) * kPanelKV + (ks % 4) * 32, 16, 1024), kIdescS,
-                                   ks > 0 ? 1u : 0u);
-                tc::mma_commit(bar_empty_k + 8 * (tile % kTcStagesK));  // the K tile has been consumed
-                tc::mma_commit(bar_s);
-            };
-            auto issue_pv = [&](uint32_t tile) {  // O (+)= P * V, 16 keys per MMA
+                    for (int ks = 0; ks < 16; ++ks)  // 16 halfs of the contraction per MMA
+                        tc::mma_f16_ts(tmem + kTmemS, tmem + kTmemQ + 8 * ks,
+                                       tc::smem_desc(kst + ((ks % 8) / 4) * kPanelKV + (ks % 4) * 32, 16, 1024), kIdescS,
+                                       ks > 0 ? 1u : 0u);
+                    tc::mma_commit(bar_empty_k + 8 * (tile % kTcStagesK));  // the K tile has been consumed
+                    tc::mma_commit(bar_s);
+                    TC_TRACE(p, tile * 8 + 7);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == kTcPvWarp) {
+        // ---------------- value MMAs: a second lane issues O (+)= P * V, 16 keys per MMA, as soon as a tile's weights
+        // are stored and its V tile has landed; the two issuers meet only through the barriers, so a tile's value
+        // product and the next tile's scores are handed to the tensor core without waiting for one another.
+        if (lane == 0 && ntiles > 0) {
+            constexpr uint32_t kIdescO = tc::instr_desc_f16(128, D, true);
+            for (uint32_t tile = 0; tile < ntiles; ++tile) {
+                if (*abort_flag != 0) break;
+                if (!wait_or_abort(bar_p + 8 * (tile & 1u), (tile >> 1) & 1u, abort_flag)) break;
+                if (!wait_or_abort(bar_full_v + 8 * (tile % kTcStagesV), (tile / kTcStagesV) & 1u, abort_flag)) break;
+                tc::fence_proxy_async();
+                tc::fence_after_sync();
+                TC_TRACE(p, tile * 8 + 1);
                 const uint32_t vst = vbuf + (tile % kTcStagesV) * kStageBytes;
                 const uint32_t a = tmem + kTmemP + (tile & 1u) * (kTcTile / 2);
 #pragma unroll
@@ -392,36 +419,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                                    (tile > 0 || j > 0) ? 1u : 0u);
                 tc::mma_commit(bar_empty_v + 8 * (tile % kTcStagesV));  // the V tile has been consumed
                 tc::mma_commit(bar_o + 8 * (tile & 1u));
-            };
-            if (wait_or_abort(bar_q, 0u, abort_flag) && wait_or_abort(bar_full_k, 0u, abort_flag)) {
-                tc::fence_proxy_async();  // the tile was written through the generic proxy (cp.async)
-                tc::fence_after_sync();
-                TC_TRACE(p, 0);
-                issue_qk(0);
-                TC_TRACE(p, 7);
-                for (uint32_t tile = 0; tile < ntiles; ++tile) {
-                    if (*abort_flag != 0) break;
-                    if (tile + 1 < ntiles) {
-                        // The next tile's scores run underneath this tile's softmax, as soon as every softmax
-                        // thread has taken this tile's scores into registers.
-                        if (!wait_or_abort(bar_full_k + 8 * ((tile + 1) % kTcStagesK), ((tile + 1) / kTcStagesK) & 1u,
-                                           abort_flag))
-                            break;
-                        if (!wait_or_abort(bar_sfree, tile & 1u, abort_flag)) break;
-                        tc::fence_proxy_async();
-                        tc::fence_after_sync();
-                        TC_TRACE(p, (tile + 1) * 8 + 0);
-                        issue_qk(tile + 1);
-                        TC_TRACE(p, (tile + 1) * 8 + 7);
-                    }
-                    if (!wait_or_abort(bar_p + 8 * (tile & 1u), (tile >> 1) & 1u, abort_flag)) break;
-                    if (!wait_or_abort(bar_full_v + 8 * (tile % kTcStagesV), (tile / kTcStagesV) & 1u, abort_flag)) break;
-                    tc::fence_proxy_async();
-                    tc::fence_after_sync();
-                    TC_TRACE(p, tile * 8 + 1);
-                    issue_pv(tile);
-                    TC_TRACE(p, tile * 8 + 2);
-                }
+                TC_TRACE(p, tile * 8 + 2);
             }
         }
         __syncwarp();
@@ -499,8 +497,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         bool done = ntiles > 0;  // every product into O has completed (nothing to wait for when there is no tile)
         for (uint32_t tile = 0; tile < ntiles; ++tile) {
             if (__any_sync(0xffffffffu, *abort_flag != 0)) { done = false; break; }
-            // The scores of this tile are complete, and so is every MMA issued before them (up to P * V of
-            // tile - 2, which read the P buffer this tile writes).
+            // The scores of this tile are complete.
             if (!__all_sync(0xffffffffu, wait_or_abort(bar_s, tile & 1u, abort_flag))) { done = false; break; }
             tc::fence_after_sync();
             if (tid == 0) TC_TRACE(p, tile * 8 + 3);
@@ -563,6 +560,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             }
             l *= corr;
             m_use = m_new;
+            // The weights of this tile go where those of tile - 2 were: that tile's value product must have read
+            // them (the score issuer no longer vouches for it, the two kinds of MMA come from different threads).
+            if (tile >= 2) {
+                if (!__all_sync(0xffffffffu, wait_or_abort(bar_o + 8 * (tile & 1u), ((tile - 2) >> 1) & 1u, abort_flag))) {
+                    done = false;
+                    break;
+                }
+                tc::fence_after_sync();
+            }
             const float neg_m = (m_use == -INFINITY) ? 0.f : -m_use;
             const uint32_t tP = tmem + lane_base + kTmemP + (tile & 1u) * (kTcTile / 2) + col0 / 2;
 #pragma unroll
