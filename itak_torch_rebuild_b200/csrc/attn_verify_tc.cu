@@ -175,6 +175,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t ntiles = (span + kTcTile - 1) / kTcTile;
 
     if (tid == 0) TC_TRACE(p, 256);
+    // Launched as a programmatic dependent of the previous kernel in the stream (AttnLaunch::pdl): this grid's CTAs are
+    // placed as SMs free up instead of after the previous grid has drained and a launch has crossed the bus; nothing
+    // is read or written before the previous kernel's memory is visible.
+    if (p.pdl != 0) {
+        asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    }
     // The query rows are requested first of all (each softmax warp a quarter of the CTA's PC distinct rows, lane l
     // the 16-byte chunk l of a row), so that their latency runs underneath the set-up below instead of behind the
     // opening burst of K/V tile loads.
@@ -770,10 +777,19 @@ cudaError_t launch_verify_tc(const AttnLaunch& p, cudaStream_t s, uint64_t* laun
     if (p.layer.head_dim != static_cast<uint32_t>(kTcD)) return cudaErrorInvalidValue;
     const uint32_t pchunks = verify_tc_pair_chunks(p.rows, p.group);
     const dim3 grid(p.splits, p.layer.kv_heads * p.gchunks * pchunks, p.n_seqs);
-    if (tc_pairs_for(p.rows, p.group) == 32)
-        verify_tc_kernel<32><<<grid, kTcThreads, kTcSmemBytes, s>>>(p);
-    else
-        verify_tc_kernel<64><<<grid, kTcThreads, kTcSmemBytes, s>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = kTcSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl != 0 ? 1 : 0;
+    const cudaError_t e = tc_pairs_for(p.rows, p.group) == 32 ? cudaLaunchKernelEx(&cfg, verify_tc_kernel<32>, p)
+                                                              : cudaLaunchKernelEx(&cfg, verify_tc_kernel<64>, p);
+    if (e != cudaSuccess) return e;
     if (launches) *launches += 1;
     return cudaGetLastError();
 }

@@ -350,6 +350,7 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                 p.v_new = d_v_new + static_cast<size_t>(at) * rows * b->row_len();
             }
             b->status_pending = true;
+            p.pdl = b->use_pdl ? 1u : 0u;
 #ifdef ITK_DECODE_TRACE
             p.trace = g_trace;
 #endif

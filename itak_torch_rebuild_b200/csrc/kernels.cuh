@@ -92,7 +92,7 @@ struct AttnLaunch {
     const float* k_new;      // decode and tcgen05 multi-row kernels: when set, the launch's new K rows
     const float* v_new;      // [n_seqs][rows][kv_heads][D] (f32); the kernel stores them at positions q_pos0.. itself
                              // instead of a separate append launch
-    uint32_t pdl;            // decode kernel launched as a programmatic dependent of the previous kernel in the
+    uint32_t pdl;            // decode and tcgen05 multi-row kernels launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
