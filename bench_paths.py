@@ -57,7 +57,6 @@ def run_prefix_restore(args, sampler_cls):
     for w in range(max(args.warmup, 3)):
         be.install_prefix_snapshot(snap, slot=w % SESSIONS)
     torch.cuda.synchronize()
-    be.profile_enable(args.steps + 8)
     launches0 = be.stats()["kernel_launches"]
     sampler = sampler_cls(0)
     sampler.start()
@@ -69,9 +68,13 @@ def run_prefix_restore(args, sampler_cls):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1) / args.steps
+    launches = be.stats()["kernel_launches"] - launches0
+    # the kernel's own duration for the roofline: the same restores once more with an event pair around each launch
+    be.profile_enable(args.steps + 8)
+    for s in range(args.steps):
+        be.install_prefix_snapshot(snap, slot=s % SESSIONS)
     prof = be.profile_read()
     be.profile_enable(0)
-    launches = be.stats()["kernel_launches"] - launches0
     # capture (the gather direction), timed the same way
     be.profile_enable(8)
     caps = [be.capture_prefix_snapshot(slot=i) for i in range(4)]
@@ -103,7 +106,8 @@ def run_prefix_restore(args, sampler_cls):
 def run_spec_verify(args, sampler_cls):
     import numpy as np
 
-    rounds = args.warmup + args.steps + 2
+    prof_steps = min(args.steps, 8)
+    rounds = max(args.warmup, 3) + args.steps + prof_steps + 2
     torch, dev, be, stream, gen, layers = _setup(args, rounds)
     snap = be.capture_prefix_snapshot(slot=SESSIONS)
     slots = list(range(SESSIONS))
@@ -138,7 +142,6 @@ def run_spec_verify(args, sampler_cls):
     for w in range(max(args.warmup, 3)):
         one_round(w, False)
     torch.cuda.synchronize()
-    be.profile_enable(args.steps * layers * 2 + 8)
     launches0 = be.stats()["kernel_launches"]
     sampler = sampler_cls(0)
     sampler.start()
@@ -150,9 +153,16 @@ def run_spec_verify(args, sampler_cls):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms = ev0.elapsed_time(ev1) / args.steps
+    launches = be.stats()["kernel_launches"] - launches0
+    timed_bytes = kv_bytes
+    # The kernel's own duration for the roofline: the same rounds once more with a CUDA-event pair around every
+    # launch (the pairs sit between consecutive kernels, so they stay out of the timed region above).
+    be.profile_enable(prof_steps * layers * 2 + 8)
+    for s in range(prof_steps):
+        one_round(args.warmup + args.steps + s, False)
     prof = be.profile_read()
     be.profile_enable(0)
-    launches = be.stats()["kernel_launches"] - launches0
+    kv_bytes = timed_bytes
     peak, src = _peak()
     a_ms = prof["attention_ms"] / max(prof["attention_launches"], 1)
     bytes_launch = kv_bytes / args.steps / layers

@@ -2,6 +2,7 @@
 geometries, and sweeps over context length, KV split count, head grouping and cache element type.
 
 Tolerance (stated by the task): max-abs error <= 1e-4 (f32 cache) or 2e-3 (f16 cache) of the output norm."""
+import ctypes as C
 import os
 
 import numpy as np
@@ -296,3 +297,47 @@ def test_batched_slots_with_ragged_lengths():
             refs[slot].append(0, stored(k[i], KvDtype.F16), stored(v[i], KvDtype.F16), positions[i])
             want = orc.gqa_attention(q[i], 1, hq, [positions[i]], refs[slot].view(0))
             assert_attention_close(got[i], want, hq, d, KvDtype.F16, f"step {step} slot {slot}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [1, 5])
+def test_pinned_host_buffers_give_the_staged_result(dtype, rows):
+    """The host-buffer call takes pageable and pinned host buffers alike (the bench's end-to-end leg passes pinned
+    ones by raw pointer): same kernels, same inputs, so the outputs are equal, and so are the rows the calls stored."""
+    import torch
+
+    hq, hkv, d, n = 32, 8, 128, 700
+    rng = np.random.default_rng(rows + 17)
+    k0 = rng.standard_normal((n, hkv * d)).astype(np.float32)
+    v0 = rng.standard_normal((n, hkv * d)).astype(np.float32)
+    outs, views = [], []
+    for pinned in (False, True):
+        gpu, _ = make_pair([0], hq, hkv, d, dtype=dtype, max_context=n + 32, chunk_cap=8)
+        gpu.append_rows(0, k0, v0, 0)
+        r2 = np.random.default_rng(99)
+        pos = n
+        got = []
+        for step in range(3):
+            q = r2.standard_normal((rows, hq * d)).astype(np.float32)
+            k = r2.standard_normal((rows, hkv * d)).astype(np.float32)
+            v = r2.standard_normal((rows, hkv * d)).astype(np.float32)
+            if pinned:
+                tq, tk, tv = (torch.from_numpy(a).pin_memory() for a in (q, k, v))
+                to = torch.empty(rows * hq * d, dtype=torch.float32).pin_memory()
+                sl, ps = (C.c_uint32 * 1)(0), (C.c_uint64 * 1)(pos)
+                gpu.attention_batch_ptrs(0, sl, ps, 1, rows, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), to.data_ptr(),
+                                         device=False)
+                got.append(to.numpy().copy())
+            else:
+                got.append(gpu.attention_batch(0, [0], [pos], rows, q, k, v).copy())
+            pos += rows
+        outs.append(np.concatenate(got))
+        views.append(gpu.view(0))
+    assert np.all(np.isfinite(outs[1]))
+    assert attention_error_max(outs[0], outs[1], hq, d) <= 1e-6
+    assert views[0][1].tobytes() == views[1][1].tobytes() and views[0][2].tobytes() == views[1][2].tobytes()
+
+
+def attention_error_max(a, b, hq, d):
+    a, b = a.reshape(-1, hq, d), b.reshape(-1, hq, d)
+    return float(np.max(np.abs(a - b).max(axis=2) / np.maximum(np.linalg.norm(b, axis=2), 1e-30)))
