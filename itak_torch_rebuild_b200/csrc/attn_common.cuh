@@ -79,12 +79,16 @@ __device__ __forceinline__ void store_out4(const AttnLaunch& p, size_t off4, flo
 // After a cell's output went out: make it visible system-wide, then count it on every rank.
 __device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p) {
     if (p.gather.n_peers == 0) return;
-    __threadfence_system();
+    // The CTA's stores are ordered before the barrier, and one thread's system-scope fence after it is cumulative
+    // over them (the grid-barrier idiom): one fence per CTA instead of one per thread.  Then a reduction per peer
+    // (no value comes back, so nothing waits for another NVLink round trip).
     __syncthreads();
-    // one thread per peer, and a reduction (no value comes back, so nothing waits for the NVLink round trip)
-    if (threadIdx.x < p.gather.n_peers)
-        asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[threadIdx.x] + p.gather.my_rank)
-                     : "memory");
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        ITK_TRACE(p, 15);  // (timeline build) the system-scope fence has returned
+        for (uint32_t j = 0; j < p.gather.n_peers; ++j)
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[j] + p.gather.my_rank) : "memory");
+    }
 }
 
 constexpr uint32_t kFusedSumMinParts = 13;  // cells shared by more parts than one register batch take the fused sum
@@ -202,10 +206,10 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
             atomicOr(p.acc_flag + cell, 1u);
         }
     }
-    __threadfence();
     __syncthreads();
     ITK_TRACE(p, 8);
     if (tid == 0) {
+        __threadfence();  // cumulative over the CTA's stores and reductions above (ordered before the barrier)
         const unsigned int ticket = atomicAdd(p.tickets + cell, 1u);
         *s_flag = (ticket == n_parts - 1) ? 1 : 0;
     }

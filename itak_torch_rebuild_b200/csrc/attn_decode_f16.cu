@@ -273,6 +273,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             }
         }
         __syncthreads();
+        ITK_TRACE(p, 14);
     }
 
     uint32_t qa[KS][4];

@@ -12,6 +12,7 @@
 //     Cache::position(): crates/cpu-compute/src/cpu.rs:558-581.
 #include <atomic>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -28,6 +29,10 @@ cudaError_t configure_verify_f16();
 cudaError_t configure_verify_tc();
 uint32_t verify_pair_chunks(uint32_t rows, uint32_t group);
 }
+
+#ifdef ITK_DECODE_TRACE
+extern "C" int itk_debug_trace_buffer(void** dev_ptr, uint64_t* bytes);
+#endif
 
 namespace {
 
@@ -806,6 +811,13 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
     ITK_CUDA(b, cudaMemcpyAsync(b->d_states, states.data(), n_seqs * sizeof(itk::SeqState), cudaMemcpyHostToDevice,
                                 b->stream), "sequence-state upload");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
+#ifdef ITK_DECODE_TRACE
+    if (!g_trace && std::getenv("ITK_TRACE_DUMP")) {  // timeline build: allocate before any capture begins
+        void* ptr;
+        uint64_t bytes;
+        itk_debug_trace_buffer(&ptr, &bytes);
+    }
+#endif
     b->res_active = true;
     b->res_slots.assign(slots, slots + n_seqs);
     b->res_max_steps = max_steps;
@@ -988,6 +1000,20 @@ int itk_resident_end(itk_backend* b, uint64_t steps_done) {
     b->stats.rows_appended += steps_done * b->res_slots.size() * b->cfg.n_layers;
     b->stats.attention_calls += steps_done * b->cfg.n_layers;
     b->res_active = false;
+#ifdef ITK_DECODE_TRACE
+    if (const char* path = std::getenv("ITK_TRACE_DUMP")) {  // timeline build: the last step's stamps, raw u64
+        if (g_trace) {
+            cudaStreamSynchronize(b->stream);
+            std::vector<unsigned long long> host(64ull * 512 * 16);
+            cudaMemcpy(host.data(), g_trace, host.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+            const std::string name = std::string(path) + "." + std::to_string(b->cfg.device);
+            if (FILE* f = std::fopen(name.c_str(), "wb")) {
+                std::fwrite(host.data(), sizeof(unsigned long long), host.size(), f);
+                std::fclose(f);
+            }
+        }
+    }
+#endif
     return ITK_OK;
 }
 
