@@ -145,3 +145,59 @@ def test_config3_continuous_batching_with_retire_and_refill():
         for layer in range(layers):
             assert gpu.next_position(layer, slot=slot) == lens[slot]
         assert_view_equal(gpu, refs[slot], 1, dtype, slot=slot)
+
+
+@pytest.mark.parametrize("hq,hkv", [(64, 8), (8, 1)])
+def test_config5_long_context_decode_at_full_context(hq, hkv):
+    """The long-context configuration's per-layer shape at its full size - batch 8, context 32768, head dim 128, f16
+    cache - with all 8 KV heads (one GPU holding the whole layer: 1 GiB per launch, the equal-run plan) and with one KV
+    head (what one of 8 GPUs holds: 128 MiB, the cell-aligned plan with the parts summed in L2), through the
+    replayable decode loop the bench uses.  The cache is prefilled on the device with seeded N(0,1) rows; the oracle
+    is fed what the device holds (read back through the view) for two of the eight sequences and checked on two
+    steps: attention to 2e-3 of the norm, and the rows the steps stored bit for bit."""
+    import torch
+
+    from kvparity import as_f32, attention_error
+
+    d, seqs, ctx, steps, layers = 128, 8, 32768, 2, 1
+    dtype = KvDtype.F16
+    dev = torch.device("cuda", 0)
+    gpu = CudaCompute(layers, hq, hkv, d, n_slots=seqs, max_context=ctx + 8, chunk_cap=1, kv_dtype=dtype)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    slots = list(range(seqs))
+    kb = torch.empty((seqs, 4096, hkv * d), device=dev)
+    vb = torch.empty_like(kb)
+    for at in range(0, ctx, 4096):
+        kb.normal_(generator=gen)
+        vb.normal_(generator=gen)
+        gpu.append_rows_device(0, slots, [at] * seqs, 4096, kb.data_ptr(), vb.data_ptr())
+    torch.cuda.synchronize()
+    sampled = (0, 5)
+    refs = {}
+    for s in sampled:
+        first, k, v = gpu.view(0, slot=s)
+        assert first == 0 and k.shape[0] == ctx
+        refs[s] = orc.KvCache([orc.GLOBAL], hkv, d)
+        refs[s].restore_bulk(0, 0, as_f32(k, dtype), as_f32(v, dtype))
+    q = torch.randn((steps, seqs, hq * d), device=dev, generator=gen)
+    kn = torch.randn((steps, seqs, hkv * d), device=dev, generator=gen)
+    vn = torch.randn((steps, seqs, hkv * d), device=dev, generator=gen)
+    out = torch.empty((seqs, hq * d), device=dev)
+    gpu.resident_begin(slots, steps)
+    worst = 0.0
+    for step in range(steps):
+        gpu.resident_layer(0, q[step].data_ptr(), kn[step].data_ptr(), vn[step].data_ptr(), out.data_ptr())
+        gpu.resident_advance()
+        gpu.synchronize()
+        got = out.cpu().numpy()
+        for s in sampled:
+            refs[s].append(0, stored(kn[step, s].cpu().numpy(), dtype), stored(vn[step, s].cpu().numpy(), dtype), ctx + step)
+            want = orc.gqa_attention(q[step, s].cpu().numpy(), 1, hq, [ctx + step], refs[s].view(0))
+            err = attention_error(got[s], want, hq, d)
+            assert err <= 2e-3, f"step {step} sequence {s}: {err:.3e}"
+            worst = max(worst, err)
+    gpu.resident_end(steps)
+    assert worst < 1e-5, "f32-grade products should sit far inside the f16-cache tolerance"
+    for s in sampled:
+        assert_view_equal(gpu, refs[s], 0, dtype, slot=s)
