@@ -125,3 +125,41 @@ def test_prep_refusals_leave_state_untouched():
     assert gpu.next_position(0) == 0 and gpu.stored_len(0) == 0
     gpu.attention_prep(0, q, k, v, pos)
     assert gpu.next_position(0) == 1
+
+
+@pytest.mark.parametrize("dtype", [KvDtype.F32, KvDtype.F16])
+@pytest.mark.parametrize("sliding,seed", [(True, 91), (False, 97)])
+def test_reference_fused_preparation_cases(dtype, sliding, seed):
+    """The two cases the reference checks its fused preparation with
+    (crates/wgpu-compute/tests/fused_kernels.rs:68-108, 433-441): 3 rows, 4 query / 2 KV heads, head dim 64, rows
+    starting at position 7, base 500000, eps 1e-5, weights lcg + 1, inputs from the test's generator; the sliding case
+    has a ring of 8 slots, so the rows land in slots 7, 0, 1.  There the fused kernel is compared with the unfused
+    chain; here the device path is compared with the CPU functions that chain stands for."""
+    rows, hq, hkv, d, start, base, eps = 3, 4, 2, 64, 7, 500000.0, 1e-5
+    window = [5] if sliding else [0]  # ring = window + chunk_cap = 8
+    gpu, (ref,) = make_pair(window, hq, hkv, d, dtype=dtype, max_context=16, chunk_cap=3)
+    q = orc.lcg(seed, rows * hq * d).reshape(rows, -1)
+    k = orc.lcg(seed + 1, rows * hkv * d).reshape(rows, -1)
+    v = orc.lcg(seed + 2, rows * hkv * d).reshape(rows, -1)
+    q_w = orc.lcg(seed + 3, d) + np.float32(1.0)
+    k_w = orc.lcg(seed + 4, d) + np.float32(1.0)
+    # positions 0..6 first (prepared rows of any content), so that the case's rows start at 7
+    fill_k, fill_v = orc.lcg(seed + 5, start * hkv * d).reshape(start, -1), orc.lcg(seed + 6, start * hkv * d).reshape(start, -1)
+    for p in range(start):
+        gpu.append(0, fill_k[p], fill_v[p], p)
+        ref.append(0, stored(fill_k[p], dtype), stored(fill_v[p], dtype), p)
+    gpu.set_layer_prep(0, q_norm_weight=q_w, k_norm_weight=k_w, norm_eps=eps, rope_base=base)
+    pos = PositionCache()
+    pos.advance(start)
+    got = gpu.attention_prep(0, q, k, v, pos)
+    qp = orc.prepare_rows(q, hq, d, start, weight=q_w, eps=eps, rope_base=base)
+    kp = orc.prepare_rows(k, hkv, d, start, weight=k_w, eps=eps, rope_base=base)
+    # the CPU cache's ring is the window itself, so the oracle goes row by row as the CPU backend does
+    # (crates/cpu-compute/src/cpu.rs:592-646); the device ring has the chunk's headroom and takes the rows at once
+    kp, qp = kp.reshape(rows, -1), qp.reshape(rows, -1)
+    want = []
+    for r in range(rows):
+        ref.append(0, stored(kp[r], dtype), stored(v[r], dtype), start + r)
+        want.append(orc.gqa_attention(qp[r], 1, hq, [start + r], ref.view(0)))
+    assert_attention_close(got, np.concatenate(want), hq, d, dtype, "fused preparation case")
+    assert_prepared_rows_close(gpu, ref, 0, dtype)
