@@ -159,7 +159,10 @@ __device__ __forceinline__ void finish_weights(const float* all_ml, uint32_t n_p
 // of every split (which become per-split weights in `wscratch`, shared memory,
 // 2 * MAXP * 8 + 8 floats) and the first batch of partial outputs are requested
 // together; every output channel is then a weighted sum over splits.
-// The ticket counter is left at zero for the next launch.
+// With AttnLaunch::acc_o set, a cell shared by more than kFusedSumMinParts CTAs
+// is summed in L2 instead (see below) and the last arrival reads one
+// accumulator rather than every part.
+// The ticket counter (and the accumulator) is left at zero for the next launch.
 template <int THREADS, int MAXP>
 __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t n_parts,
                                             uint32_t part, uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
