@@ -212,6 +212,16 @@ int itk_attention_batch_prep_device(itk_backend* b, uint32_t layer, uint32_t n_s
  *   itk_resident_advance  queues the kernel that moves every listed slot to the next position (end of a step)
  *   itk_resident_end      tells the backend how many steps actually ran, and leaves the mode
  * Between begin and end no other call may touch the listed slots. */
+/* How the replayable loop's decode launch cuts its work: for `n_seqs` sequences of keys[] visible keys, each with
+ * `cells_per_seq` (KV head x head chunk) cells of ceil(keys / 64) tiles, across `ctas` persistent CTAs with `splits`
+ * partial slots per cell.  *aligned = 1 when every cell gets a whole number of CTAs of its own (no CTA crosses a cell
+ * boundary), 0 for equal contiguous runs over all cells laid end to end.  runs[cta] = {sequence, cell within the
+ * sequence, first tile, tiles walked (0 = idle), CTAs sharing the first cell, this CTA's number among them}; a run
+ * that ends a cell goes on with the next cell's first tile.  Host arithmetic only - the same functions the kernel
+ * evaluates - so that the partition can be checked without a GPU.  No counterpart in the reference, whose kernels
+ * take one workgroup per (row, head) (crates/wgpu-compute/src/kernels/k6_attention.rs:286-296). */
+int itk_decode_plan(const uint32_t* keys, uint32_t n_seqs, uint32_t cells_per_seq, uint32_t ctas, uint32_t splits,
+                    uint32_t* aligned, uint32_t* runs);
 int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, uint64_t max_steps);
 int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
                        float* d_out);

@@ -113,6 +113,7 @@ SIGNATURES = {
     "itk_layer_prep_set": (C.c_int, [_vp, _u32, C.POINTER(PrepConfig)]),
     "itk_attention_batch_prep": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_attention_batch_prep_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
+    "itk_decode_plan": (C.c_int, [_u32p, _u32, _u32, _u32, _u32, _u32p, _u32p]),
     "itk_resident_begin": (C.c_int, [_vp, _u32, _u32p, _u64]),
     "itk_resident_layer": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "itk_resident_advance": (C.c_int, [_vp]),

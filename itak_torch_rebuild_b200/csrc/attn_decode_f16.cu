@@ -173,35 +173,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         }
     };
     TileCursor lc;  // load cursor, runs STAGES - 1 tiles ahead of the compute cursor
-    uint32_t ntiles = 0;
-    uint32_t al_parts = 0, al_part = 0;  // aligned plan: CTAs sharing this CTA's cell, and which of them this is
-    if (aligned) {
-        if (blockIdx.x < abase[p.n_seqs]) {
-            uint32_t s = 0;
-            while (abase[s + 1] <= blockIdx.x) ++s;
-            lc.seq = s;
-            enter_seq(lc);
-            const uint32_t ns = (abase[s + 1] - abase[s]) / HY;
-            const uint32_t r = blockIdx.x - abase[s];
-            const uint32_t run = (lc.T + ns - 1) / ns;
-            lc.hy = r / ns;
-            al_part = r % ns;
-            al_parts = (lc.T + run - 1) / run;
-            lc.tile = al_part * run;
-            if (lc.tile < lc.T) ntiles = min(run, lc.T - lc.tile);
-        }
-    } else {
-        const uint32_t g0 = blockIdx.x * per;
-        if (g0 < total) {
-            ntiles = min(total, g0 + per) - g0;
-            uint32_t s = 0;
-            while (s + 1 < p.n_seqs && cum[s + 1] <= g0) ++s;
-            lc.seq = s;
-            enter_seq(lc);
-            const uint32_t r = g0 - cum[s];
-            lc.hy = r / lc.T;
-            lc.tile = r % lc.T;
-        }
+    const DecodeRun my = decode_cta_run(aligned, blockIdx.x, sn, cum, abase, p.n_seqs, HY, per);
+    const uint32_t ntiles = my.ntiles;
+    const uint32_t al_parts = my.parts, al_part = my.part;  // aligned plan: CTAs sharing this CTA's cell, and which
+    if (ntiles != 0) {
+        lc.seq = my.seq;
+        enter_seq(lc);
+        lc.hy = my.hy;
+        lc.tile = my.tile;
     }
     if (ntiles == 0) {
         if (p.pdl == 2) pdl_wait();
@@ -508,12 +487,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             // which CTAs share this cell, and which of them this one is
             if (i + 1 == ntiles) ITK_TRACE(p, 13);
             uint32_t n_parts = al_parts, part = al_part;
-            if (!aligned) {
-                const uint32_t gs = cum[cc.seq] + cc.hy * cc.T;
-                const uint32_t first = gs / per, last = (gs + cc.T - 1) / per;
-                n_parts = last - first + 1;
-                part = blockIdx.x - first;
-            }
+            if (!aligned) decode_cell_parts(blockIdx.x, cum[cc.seq] + cc.hy * cc.T, cc.T, per, &n_parts, &part);
             finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm, fl, flag,
                                                          wscratch);
             fresh = true;

@@ -715,6 +715,42 @@ int itk_get_stats(const itk_backend* b, itk_stats* out) {
     return ITK_OK;
 }
 
+int itk_decode_plan(const uint32_t* keys, uint32_t n_seqs, uint32_t cells_per_seq, uint32_t ctas, uint32_t splits,
+                    uint32_t* aligned, uint32_t* runs) {
+    if (!keys || !aligned || !runs || n_seqs == 0 || n_seqs > static_cast<uint32_t>(itk::kMaxSeqsPerLaunch) ||
+        cells_per_seq == 0 || ctas == 0)
+        return ITK_ERR_INVALID_ARGUMENT;
+    std::vector<uint32_t> cum(n_seqs + 1), first(n_seqs + 1);
+    uint64_t total = 0;
+    for (uint32_t s = 0; s < n_seqs; ++s) {
+        if (keys[s] == 0) return ITK_ERR_INVALID_ARGUMENT;
+        cum[s] = static_cast<uint32_t>(total);
+        total += static_cast<uint64_t>((keys[s] + 63u) / 64u) * cells_per_seq;
+        if (total > 0xffffffffull) return ITK_ERR_INVALID_ARGUMENT;
+    }
+    cum[n_seqs] = static_cast<uint32_t>(total);
+    const uint32_t per = static_cast<uint32_t>((total + ctas - 1) / ctas);
+    uint32_t worst = 0;
+    const bool al = itk::decode_aligned_plan(keys, n_seqs, cells_per_seq, ctas, static_cast<uint32_t>(total), per, splits,
+                                             first.data(), &worst);
+    *aligned = al ? 1u : 0u;
+    for (uint32_t c = 0; c < ctas; ++c) {
+        itk::DecodeRun r = itk::decode_cta_run(al, c, keys, cum.data(), first.data(), n_seqs, cells_per_seq, per);
+        if (!al && r.ntiles != 0) {
+            const uint32_t T = (keys[r.seq] + 63u) / 64u;
+            itk::decode_cell_parts(c, cum[r.seq] + r.hy * T, T, per, &r.parts, &r.part);
+        }
+        uint32_t* o = runs + 6ull * c;
+        o[0] = r.seq;
+        o[1] = r.hy;
+        o[2] = r.tile;
+        o[3] = r.ntiles;
+        o[4] = r.parts;
+        o[5] = r.part;
+    }
+    return ITK_OK;
+}
+
 int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, uint64_t max_steps) {
     if (!b || !slots) return ITK_ERR_INVALID_ARGUMENT;
     cudaSetDevice(b->cfg.device);

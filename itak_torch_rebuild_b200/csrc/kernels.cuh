@@ -219,6 +219,53 @@ __host__ __device__ inline bool decode_aligned_plan(const uint32_t* keys, uint32
     const uint32_t slack = per / 16u > 1u ? per / 16u : 1u;
     return ok && w <= per + slack;
 }
+// Where a CTA of the decode kernel starts and how far it walks.  `cum[s]` = tiles of all cells before sequence s
+// (cum[n_seqs] = total), `first_cta` from decode_aligned_plan, `per` = tiles per CTA of the equal-run plan.
+// ntiles == 0: the CTA has nothing to do.  parts / part (how many CTAs share the first cell, and which of them
+// this is) are filled for the aligned plan only; in the equal-run plan a cell's parts follow from decode_cell_parts.
+struct DecodeRun {
+    uint32_t seq, hy, tile, ntiles, parts, part;
+};
+__host__ __device__ inline DecodeRun decode_cta_run(bool aligned, uint32_t cta, const uint32_t* keys, const uint32_t* cum,
+                                                    const uint32_t* first_cta, uint32_t n_seqs, uint32_t cells_per_seq,
+                                                    uint32_t per) {
+    DecodeRun r{0, 0, 0, 0, 0, 0};
+    if (aligned) {
+        if (cta >= first_cta[n_seqs]) return r;
+        uint32_t s = 0;
+        while (first_cta[s + 1] <= cta) ++s;
+        const uint32_t T = (keys[s] + 63u) / 64u;
+        const uint32_t ns = (first_cta[s + 1] - first_cta[s]) / cells_per_seq;
+        const uint32_t at = cta - first_cta[s];
+        const uint32_t run = (T + ns - 1) / ns;
+        r.seq = s;
+        r.hy = at / ns;
+        r.part = at % ns;
+        r.parts = (T + run - 1) / run;
+        r.tile = r.part * run;
+        if (r.tile < T) r.ntiles = (run < T - r.tile) ? run : T - r.tile;
+        return r;
+    }
+    const uint32_t total = cum[n_seqs];
+    const uint64_t g0 = static_cast<uint64_t>(cta) * per;
+    if (g0 >= total) return r;
+    r.ntiles = static_cast<uint32_t>((total < g0 + per ? total : g0 + per) - g0);
+    uint32_t s = 0;
+    while (s + 1 < n_seqs && cum[s + 1] <= g0) ++s;
+    const uint32_t T = (keys[s] + 63u) / 64u;
+    const uint32_t at = static_cast<uint32_t>(g0) - cum[s];
+    r.seq = s;
+    r.hy = at / T;
+    r.tile = at % T;
+    return r;
+}
+// Equal-run plan: the CTAs that share cell (seq, hy) of T tiles, and which of them `cta` is.
+__host__ __device__ inline void decode_cell_parts(uint32_t cta, uint32_t cell_first_tile, uint32_t T, uint32_t per,
+                                                  uint32_t* parts, uint32_t* part) {
+    const uint32_t first = cell_first_tile / per, last = (cell_first_tile + T - 1) / per;
+    *parts = last - first + 1;
+    *part = cta - first;
+}
 // Most CTAs that can share a cell of T tiles when every CTA walks `per` tiles.
 inline uint32_t decode_parts_for(uint32_t T, uint32_t per) { return (T + per - 2) / per + 1; }
 bool decode_f16_supported(uint32_t head_dim, uint32_t rows);
