@@ -27,8 +27,7 @@ namespace itk {
 
 namespace {
 
-constexpr int kVerThreads = 128;
-constexpr int kVerWarps = 4;
+constexpr int kVerThreads = 128;  // 4 warps
 constexpr int kVerTile = 64;     // keys per tile
 constexpr int kPairsPerCta = 32; // (row, head) pairs per CTA: 8 per warp
 constexpr int kVerStages = 3;

@@ -1830,10 +1830,8 @@ int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* s, const char* mode
     for (size_t l = 0; l < n_layers; ++l) {
         const size_t elems = static_cast<size_t>(s->rows[l]) * row;
         if (elems == 0) continue;
-        float* kdst = reinterpret_cast<float*>(out + at);  // may be unaligned: filled through memcpy below
-        uint8_t* kbytes = out + at;
+        uint8_t* kbytes = out + at;  // may be unaligned for f32: filled through memcpy below
         uint8_t* vbytes = out + at + elems * sizeof(float);
-        (void)kdst;
         if (!s->f16) {
             // the payload offset is arbitrary, so download to aligned scratch and copy the bytes
             std::vector<float> tmp(2 * elems);
