@@ -263,6 +263,16 @@ int itk_draft_attention(const float* d_q, const float* d_committed_k, const floa
                         uint32_t sliding, uint32_t window, float scale, float* d_out, void* cuda_stream,
                         char* error_text, size_t error_text_len);
 
+/* The rotate half of the reference's K17 (crates/wgpu-compute/src/kernels/k17_dflash.rs:78-107, 255-271): rotates
+ * `rows` x `heads` head rows of d_x ([rows][heads][head_dim], device f32) in place, row r at d_positions[r] (device
+ * u32) - positions need not be consecutive, as an injection chunk's are not.  pairing 1 is the draft model's
+ * half-split (NeoX) form, torch_math::rope (crates/torch-math/src/rope.rs:63-117); pairing 0 is rope_interleaved.  f64
+ * angles rounded once, as the CPU functions.  Only queues work on `cuda_stream`; refusals come back as
+ * ITK_ERR_INVALID_ARGUMENT with the text in error_text. */
+int itk_rope_rows(float* d_x, const uint32_t* d_positions, uint32_t rows, uint32_t heads, uint32_t head_dim,
+                  uint32_t rotary_dim, uint32_t pairing, float base, void* cuda_stream, char* error_text,
+                  size_t error_text_len);
+
 /* gqa_attention alone (crates/attention/src/attention.rs:104-215) over what a
  * slot already holds: `rows` queries at query_positions[], host buffers.
  * Refuses ITK_ERR_NO_VISIBLE_KEYS when a query sees nothing. */

@@ -159,6 +159,7 @@ SIGNATURES = {
                                           C.POINTER(_sz)]),
     "itk_prefix_store_stats": (C.c_int, [_vp, _u64p, _u64p, _u64p]),
     "itk_prefix_store_entry": (C.c_int, [_vp, _u64, C.c_char_p, _sz, _u64p, _u64p, _u64p, _u64p, _u64p]),
+    "itk_rope_rows": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _u32, C.c_float, _vp, C.c_char_p, _sz]),
     "itk_decode_attention_noalloc": (C.c_int, [_vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32p, _u32p, _vp, _vp, _u32, _vp,
                                                C.c_char_p, _sz]),
 }

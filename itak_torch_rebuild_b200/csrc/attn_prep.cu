@@ -16,6 +16,8 @@
 // One warp owns one head row (head_dim <= 256): it sums the squares with shuffles, writes the normalised row to
 // its slice of shared memory, and every lane rotates the pairs it owns from there.  Bound: launch latency - a
 // decode step touches n_seqs x (q_heads + kv_heads) x head_dim x 8 bytes.
+#include <cstdio>
+
 #include "kernels.cuh"
 
 namespace itk {
@@ -91,6 +93,31 @@ __global__ void __launch_bounds__(kPrepWarps * 32) prep_rows_kernel(const __grid
     for (uint32_t d = rot + lane; d < D; d += 32) dst[d] = mine[d];
 }
 
+// In-place rotation of `rows` x `heads` head rows at per-row positions read from a device array: the rotate half of
+// the reference's K17 (crates/wgpu-compute/src/kernels/k17_dflash.rs:78-107), whose two call sites see different
+// position sources (an inject chunk's caller-supplied positions, a block's start..start+rows span).  One thread per
+// pair; a pair's two channels are read and written by that thread alone, so the rotation is safe in place.  Angle,
+// sine, cosine and the products in f64, rounded once (crates/torch-math/src/rope.rs:63-117).
+__global__ void rope_rows_kernel(float* x, const uint32_t* positions, uint32_t rows, uint32_t heads, uint32_t head_dim,
+                                 uint32_t rotary_dim, uint32_t pairing, double base) {
+    const uint32_t half = rotary_dim / 2;
+    const uint64_t per_row = static_cast<uint64_t>(heads) * half;
+    const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<uint64_t>(rows) * per_row) return;
+    const uint32_t row = static_cast<uint32_t>(idx / per_row);
+    const uint32_t rem = static_cast<uint32_t>(idx % per_row);
+    const uint32_t head = rem / half, i = rem % half;
+    const double angle = static_cast<double>(positions[row]) *
+                         pow(base, -static_cast<double>(2 * i) / static_cast<double>(rotary_dim));
+    double s, c;
+    sincos(angle, &s, &c);
+    float* h = x + (static_cast<size_t>(row) * heads + head) * head_dim;
+    const uint32_t a = pairing == 0 ? 2 * i : i, b = pairing == 0 ? 2 * i + 1 : i + half;
+    const double u = h[a], v = h[b];
+    h[a] = static_cast<float>(u * c - v * s);
+    h[b] = static_cast<float>(u * s + v * c);
+}
+
 }  // namespace
 
 cudaError_t launch_prep(const PrepLaunch& p, cudaStream_t s, uint64_t* launches) {
@@ -107,3 +134,33 @@ cudaError_t launch_prep(const PrepLaunch& p, cudaStream_t s, uint64_t* launches)
 }
 
 }  // namespace itk
+
+// Refusals follow check_rotate (crates/wgpu-compute/src/kernels/k17_dflash.rs:255-271) and the CPU function's own
+// (crates/torch-math/src/rope.rs:70-95), by the same names.
+extern "C" int itk_rope_rows(float* d_x, const uint32_t* d_positions, uint32_t rows, uint32_t heads, uint32_t head_dim,
+                             uint32_t rotary_dim, uint32_t pairing, float base, void* cuda_stream, char* error_text,
+                             size_t error_text_len) {
+    auto refuse = [&](const char* fmt, unsigned long long a = 0, unsigned long long b = 0) {
+        if (error_text && error_text_len) snprintf(error_text, error_text_len, fmt, a, b);
+        return 101;  // ITK_ERR_INVALID_ARGUMENT
+    };
+    if (error_text && error_text_len) error_text[0] = '\0';
+    if (rows == 0 || heads == 0) return refuse("rotate needs at least one row and head, got rows %llu, heads %llu", rows, heads);
+    if (head_dim < 2 || head_dim % 2 != 0) return refuse("head_dim %llu must be even and at least 2", head_dim);
+    if (rotary_dim < 2 || rotary_dim % 2 != 0 || rotary_dim > head_dim)
+        return refuse("rope: rotary_dim must be even, >= 2, and <= head_dim");
+    if (!(base > 1.0f) || base > 3.0e38f) return refuse("rope: base must be finite and > 1");
+    if (pairing > 1) return refuse("rope: pairing is 0 (adjacent) or 1 (half split)");
+    if (!d_x || !d_positions) return refuse("null pointer argument");
+    const unsigned long long pairs = static_cast<unsigned long long>(rows) * heads * (rotary_dim / 2);
+    const unsigned long long blocks = (pairs + 127) / 128;
+    if (blocks > 0x7fffffffull) return refuse("rows x heads x rotary_dim = %llu pairs is too large", pairs);
+    itk::rope_rows_kernel<<<static_cast<unsigned int>(blocks), 128, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        d_x, d_positions, rows, heads, head_dim, rotary_dim, pairing, static_cast<double>(base));
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        if (error_text && error_text_len) snprintf(error_text, error_text_len, "rotate launch failed: %s", cudaGetErrorString(e));
+        return 100;  // ITK_ERR_CUDA
+    }
+    return 0;
+}

@@ -94,3 +94,70 @@ def test_refusals_are_named():
     big = np.zeros((1, 300), np.float32)
     rc, msg, _ = run_device(big, 0, [], big[:0], big[:0], big, big, 1, 1, 300, 300, False, False, 0)
     assert rc == _lib.ERR_INVALID_ARGUMENT and "supported range" in msg
+
+
+class Rng:
+    """crates/wgpu-compute/tests/dflash_session.rs:46-61"""
+
+    def __init__(self, seed):
+        self.s = seed
+
+    def next_f32(self):
+        self.s = (self.s * 6364136223846793005 + 1442695040888963407) & ((1 << 64) - 1)
+        return np.float32(self.s >> 56) / np.float32(256.0) - np.float32(0.5)
+
+
+def rotate_on_device(x, positions, heads, d, rot, pairing, base):
+    import torch
+
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    dx = torch.as_tensor(np.ascontiguousarray(x, dtype=np.float32)).to(dev)
+    dp = torch.as_tensor(np.asarray(positions, dtype=np.int32), dtype=torch.int32).to(dev)
+    err = C.create_string_buffer(256)
+    rc = lib.itk_rope_rows(dx.data_ptr(), dp.data_ptr(), len(positions), heads, d, rot, pairing, base, None, err, 256)
+    torch.cuda.synchronize()
+    return rc, err.value.decode(), dx.cpu().numpy()
+
+
+def test_rotate_matches_torch_math_rope_on_the_reference_case():
+    """crates/wgpu-compute/tests/dflash_session.rs:653-700: 3 rows at positions 0, 5, 127, 2 heads, head dim 8, inputs
+    from the test's generator seeded 0x207a7e, NeoX pairing, base 10000, in place; the reference allows 1e-4 of
+    absolute drift against torch_math::rope for its f32 shader, the f64 device arithmetic gets 2 ulps."""
+    rows, heads, d = 3, 2, 8
+    positions = [0, 5, 127]
+    rng = Rng(0x207A7E)
+    x = np.array([rng.next_f32() for _ in range(rows * heads * d)], dtype=np.float32).reshape(rows, heads, d)
+    rc, msg, got = rotate_on_device(x, positions, heads, d, d, 1, 10000.0)
+    assert rc == 0, msg
+    for r, p in enumerate(positions):
+        for h in range(heads):
+            want = orc.rope(x[r, h], p, 10000.0, d)
+            assert np.max(np.abs(got[r, h] - want)) < 1e-4
+            assert np.all(np.abs(got[r, h] - want) <= 2 * np.spacing(np.abs(want)) + 1e-7)
+
+
+@pytest.mark.parametrize("pairing", [0, 1])
+@pytest.mark.parametrize("heads,d,rot", [(8, 128, 128), (4, 64, 32), (2, 256, 256)])
+def test_rotate_at_scattered_positions(pairing, heads, d, rot):
+    rng = np.random.default_rng(d + pairing)
+    positions = [0, 3, 4, 1000, 32767, 131071, 7]
+    x = rng.standard_normal((len(positions), heads, d)).astype(np.float32)
+    rc, msg, got = rotate_on_device(x, positions, heads, d, rot, pairing, 500000.0)
+    assert rc == 0, msg
+    fn = orc.rope_interleaved if pairing == 0 else orc.rope
+    for r, p in enumerate(positions):
+        for h in range(heads):
+            want = fn(x[r, h], p, 500000.0, d, rot)
+            assert np.all(np.abs(got[r, h] - want) <= 4 * np.spacing(np.abs(want)) + 1e-7), (r, h)
+
+
+def test_rotate_refusals_are_named():
+    """crates/wgpu-compute/src/kernels/k17_dflash.rs:255-271"""
+    x = np.zeros((1, 1, 8), np.float32)
+    rc, msg, _ = rotate_on_device(x, [], 1, 8, 8, 1, 10000.0)
+    assert rc == _lib.ERR_INVALID_ARGUMENT and msg == "rotate needs at least one row and head, got rows 0, heads 1"
+    rc, msg, _ = rotate_on_device(np.zeros((1, 1, 7), np.float32), [0], 1, 7, 6, 1, 10000.0)
+    assert rc == _lib.ERR_INVALID_ARGUMENT and msg == "head_dim 7 must be even and at least 2"
+    rc, msg, _ = rotate_on_device(x, [0], 1, 8, 8, 1, 1.0)
+    assert rc == _lib.ERR_INVALID_ARGUMENT and "base must be finite and > 1" in msg
