@@ -198,3 +198,23 @@ def test_put_replaces_an_entry_with_the_same_tokens(tmp_path):
     store.put(toks, snapshot_for(toks, "new").to_bytes(), 2)
     assert len(store.entries()) == 1 and store.entries()[0].created_unix == 2
     assert store.lookup(toks, expected_fingerprint="new", now=3).token_count == 3
+
+
+def test_a_taken_file_name_gets_a_counter_suffix(tmp_path):
+    """store.rs:459-502: when another token list already owns the hash/length/discriminator name (a double hash
+    collision, here planted), the put takes `-c1` and both entries serve their own prefix."""
+    tokens, squatter = [7, 7, 7], [1, 2, 3]
+    name = ops.file_name_for(tokens)
+    snap_s = snapshot_for(squatter, "m").to_bytes()
+    # a well-formed entry for `squatter` sitting under the name `tokens` would get
+    (tmp_path / name).write_bytes(ops.entry_bytes(squatter, snap_s, 5))
+    store = PrefixStore(str(tmp_path), 1 << 30)
+    assert [e.file_name for e in store.entries()] == [name]
+    store.put(tokens, snapshot_for(tokens, "m").to_bytes(), 6)
+    names = sorted(e.file_name for e in store.entries())
+    assert names == sorted([name, ops.file_name_for(tokens, counter=1)])
+    assert store.lookup(tokens, now=7).snapshot_bytes == snapshot_for(tokens, "m").to_bytes()
+    assert store.lookup(squatter, now=8).snapshot_bytes == snap_s
+    # putting the same tokens again reuses the suffixed name instead of taking `-c2`
+    store.put(tokens, snapshot_for(tokens, "m2").to_bytes(), 9)
+    assert sorted(e.file_name for e in store.entries()) == names
