@@ -136,6 +136,16 @@ const char* itk_last_error(const itk_backend* b);
  * the backend's own non-blocking stream again (pass cudaStreamLegacy for
  * CUDA's default stream).  The caller orders its own work against it. */
 int itk_set_stream(itk_backend* b, void* cuda_stream);
+/* Tuning and A/B switches of one backend, set explicitly by the caller (the library reads no environment
+ * variables); no counterpart in the reference, whose switches live in the engine's configuration
+ * (crates/itak-kv/src/config.rs).  Names: "decode_ctas" (persistent CTAs of the decode kernel, 0 = two per SM),
+ * "decode_splits" (KV splits of the general and multi-row kernels, 0 = chosen per launch), "pdl" (programmatic
+ * dependent launch inside the replayable loop, default 1), "decode_fused_sum" (cells shared by many CTAs are summed
+ * in L2, default 1), "separate_append" (decode steps launch the append kernel separately, default 0),
+ * "force_general" (multi-row calls take the CUDA-core kernel, default 0), "verify_tc" (multi-row calls take the
+ * tcgen05 kernel, default 1), "gather_poll_limit" (polls of a peer's arrival flag before the fused gather's wait
+ * gives up, default 200000).  Unknown names and out-of-range values are refused; not allowed inside a resident loop. */
+int itk_set_option(itk_backend* b, const char* name, int64_t value);
 int itk_synchronize(itk_backend* b);
 int itk_get_stats(const itk_backend* b, itk_stats* out);
 /* Per-kernel device timing, the counterpart of the reference's timestamp-query
@@ -222,6 +232,13 @@ int itk_attention_batch_prep_device(itk_backend* b, uint32_t layer, uint32_t n_s
  * take one workgroup per (row, head) (crates/wgpu-compute/src/kernels/k6_attention.rs:286-296). */
 int itk_decode_plan(const uint32_t* keys, uint32_t n_seqs, uint32_t cells_per_seq, uint32_t ctas, uint32_t splits,
                     uint32_t* aligned, uint32_t* runs);
+/* How an ordinary decode call (one row per sequence, f16 cache) cuts a batch into launches: at most
+ * *seqs_per_launch sequences go into one launch, whose (sequence, KV head x head chunk) cells then own
+ * *parts_per_cell partial slots each of the backend's split scratch of *scratch_slots slots (a cell can always be
+ * cut in two, so never fewer than 2).  ITK_ERR_CAPACITY when a single sequence's cells do not fit.  Host arithmetic
+ * only, the function the backend itself uses; no counterpart in the reference. */
+int itk_decode_batch_limits(uint32_t n_seqs, uint32_t cells_per_seq, uint32_t* seqs_per_launch, uint32_t* parts_per_cell,
+                            uint64_t* scratch_slots);
 int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, uint64_t max_steps);
 int itk_resident_layer(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
                        float* d_out);
@@ -383,12 +400,14 @@ int itk_snapshot_from_itkv(itk_backend* b, const uint8_t* bytes, size_t n, const
  *   k_layer, v_layer  device, f16 [slot][kv_heads][ring][head_dim]; keys 0..kv_len[i]-1 of sequence i
  *                     sit at rows 0.. of slot slots[i]
  *   d_q, d_out        device f32 [n_seqs][q_heads][head_dim]
- *   splits            CTAs along each key range; 0 picks one
+ *   splits            CTAs along each key range, at most 64; 0 picks one
  *   error_text        optional buffer that receives the reason of a refusal
  *
- * Limits: head_dim 64 or 128; n_seqs <= 64; n_seqs x kv_heads x ceil(group/8) x splits <= 2048.
- * Larger requests return ITK_ERR_CAPACITY.  The first call on a device looks
- * up the array's device address and sets a kernel attribute; issue that first
+ * Limits: head_dim 64 or 128; n_seqs <= 64; n_seqs x kv_heads x ceil(group/8) x max(splits, 2) <= 2048
+ * (a key range can always be cut in two, so one split still reserves two partial slots).
+ * Larger requests return ITK_ERR_CAPACITY.  k_layer, v_layer, d_q and d_out must be 16-byte aligned.
+ * The first call on a device looks up the array's device address and sets a kernel attribute (under a
+ * lock, so first calls from several host threads are safe); issue that first
  * call outside any stream capture.  All calls share the array (the counters in
  * it are cleared on the stream at the start of each call): calls that may
  * overlap on the GPU must be serialised by the caller.  The device that owns

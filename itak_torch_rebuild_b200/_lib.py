@@ -105,6 +105,7 @@ SIGNATURES = {
     "itk_backend_destroy": (None, [_vp]),
     "itk_last_error": (C.c_char_p, [_vp]),
     "itk_set_stream": (C.c_int, [_vp, _vp]),
+    "itk_set_option": (C.c_int, [_vp, C.c_char_p, C.c_int64]),
     "itk_synchronize": (C.c_int, [_vp]),
     "itk_get_stats": (C.c_int, [_vp, C.POINTER(Stats)]),
     "itk_attention": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _sz, _u64, _vp]),
@@ -114,6 +115,7 @@ SIGNATURES = {
     "itk_attention_batch_prep": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_attention_batch_prep_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_decode_plan": (C.c_int, [_u32p, _u32, _u32, _u32, _u32, _u32p, _u32p]),
+    "itk_decode_batch_limits": (C.c_int, [_u32, _u32, _u32p, _u32p, _u64p]),
     "itk_resident_begin": (C.c_int, [_vp, _u32, _u32p, _u64]),
     "itk_resident_layer": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "itk_resident_advance": (C.c_int, [_vp]),

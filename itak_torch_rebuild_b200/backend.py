@@ -120,7 +120,8 @@ class CudaCompute:
 
     def __init__(self, n_layers: int, q_heads: int, kv_heads: int, head_dim: int, *, n_slots: int = 1,
                  max_context: int = 4096, chunk_cap: int = 64, kv_dtype: KvDtype = KvDtype.F16,
-                 layer_window: Optional[Sequence[int]] = None, device: int = 0):
+                 layer_window: Optional[Sequence[int]] = None, device: int = 0,
+                 options: Optional[dict] = None):
         self._lib = _lib.load()
         self._h = None
         self.n_layers, self.q_heads, self.kv_heads, self.head_dim = n_layers, q_heads, kv_heads, head_dim
@@ -137,6 +138,12 @@ class CudaCompute:
         if rc != _lib.OK:
             raise CudaComputeError(rc, self._lib.itk_last_error(None).decode("utf-8", "replace"))
         self._h = h
+        for name, value in (options or {}).items():
+            self.set_option(name, value)
+
+    def set_option(self, name: str, value: int):
+        """A tuning or A/B switch of this backend (``itk_set_option``): e.g. ``decode_ctas``, ``verify_tc``."""
+        self._check(self._lib.itk_set_option(self._h, name.encode(), int(value)))
 
     def close(self):
         if self._h is not None:

@@ -40,6 +40,7 @@
 // far inside the f16-KV tolerance.  A 64-row tcgen05 tile would be 7/8 padding
 // here; the tensor pipe is at ~18% load either way and never the limiter.
 #include <cstdio>
+#include <mutex>
 
 #include "attn_common.cuh"
 #include "kv_convert.cuh"
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             for (;;) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(p.gather.my_flags + tid) : "memory");
                 if (seen >= target) break;
-                if (++spins > 200000u) {
+                if (++spins > p.gather.poll_limit) {
                     atomicOr(p.gather.err, 1u);
                     break;
                 }
@@ -531,7 +532,7 @@ cudaError_t launch_decode_f16(AttnLaunch p, uint32_t cta_slots, uint32_t max_par
     }
     if (total == 0 || total > 0xffffffffull) return cudaErrorInvalidValue;
     if (max_parts > kDecodeMaxParts) max_parts = kDecodeMaxParts;
-    if (max_parts < 2) max_parts = 2;
+    if (max_parts < 2) return cudaErrorInvalidValue;  // a cut cell needs two partial slots; the caller sizes the batch
     if (cta_slots == 0) cta_slots = 1;
     uint64_t ctas = total < cta_slots ? total : cta_slots;
     uint32_t per = static_cast<uint32_t>((total + ctas - 1) / ctas);
@@ -610,11 +611,11 @@ cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, 
 //  - the array below (about 8.1 MiB) exists on every GPU that loads this
 //    library, from load until the process exits, whether or not this entry
 //    point is ever used;
-//  - (sequences x KV heads x head chunks) x splits may not exceed
-//    kNoAllocCellSplits, where `splits` bounds how many CTAs may share one
-//    (sequence, head) key range (at least 2 are always reserved); sequences may
-//    not exceed 64, head_dim is 64 or 128; anything larger is refused with
-//    ITK_ERR_CAPACITY and a message;
+//  - (sequences x KV heads x head chunks) x max(splits, 2) may not exceed
+//    kNoAllocCellSplits, where `splits` (at most 64) bounds how many CTAs may
+//    share one (sequence, head) key range; sequences may not exceed 64,
+//    head_dim is 64 or 128; anything larger is refused with ITK_ERR_CAPACITY
+//    and a message;
 //  - all calls share the one array and it keeps whatever the previous call
 //    left.  The arrival counters are the only part that must read zero at
 //    launch; every call clears them on its stream first.  Two calls whose
@@ -639,8 +640,10 @@ constexpr int kNoAllocMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartO + kNoAllocPartMl + kNoAllocTickets];
 
-// Device address of g_noalloc_scratch per device ordinal, resolved on first use.
+// Device address of g_noalloc_scratch per device ordinal, resolved on first use under g_noalloc_mutex (two host
+// threads may make their first call on a device at the same time).
 void* g_noalloc_ptr[kNoAllocMaxDevices] = {};
+std::mutex g_noalloc_mutex;
 
 int noalloc_refuse(int code, char* text, size_t text_len, const char* fmt, unsigned long long a = 0,
                    unsigned long long b = 0) {
@@ -659,6 +662,10 @@ extern "C" int itk_decode_attention_noalloc(const void* k_layer, const void* v_l
     if (error_text && error_text_len) error_text[0] = '\0';
     if (!k_layer || !v_layer || !slots || !kv_len || !d_q || !d_out)
         return noalloc_refuse(101, error_text, error_text_len, "null pointer argument");
+    // the kernel moves cache rows, queries and outputs as 16-byte vectors
+    if (((reinterpret_cast<uintptr_t>(k_layer) | reinterpret_cast<uintptr_t>(v_layer) | reinterpret_cast<uintptr_t>(d_q) |
+          reinterpret_cast<uintptr_t>(d_out)) & 15u) != 0)
+        return noalloc_refuse(101, error_text, error_text_len, "k_layer, v_layer, d_q and d_out must be 16-byte aligned");
     if (kv_heads == 0 || q_heads == 0 || ring == 0)
         return noalloc_refuse(1, error_text, error_text_len, "kv_heads, q_heads and ring must be positive");
     if (q_heads % kv_heads != 0)
@@ -687,10 +694,11 @@ extern "C" int itk_decode_attention_noalloc(const void* k_layer, const void* v_l
         return noalloc_refuse(102, error_text, error_text_len,
                               "%llu (sequence, head) cells exceed the built-in scratch of %llu", cells,
                               static_cast<unsigned long long>(kNoAllocCellSplits));
-    if (splits > static_cast<uint32_t>(kMaxSplits))
+    if (splits > kDecodeMaxParts)
         return noalloc_refuse(102, error_text, error_text_len, "%llu splits exceed the kernel's maximum of %llu", splits,
-                              static_cast<unsigned long long>(kMaxSplits));
-    // `splits` bounds the CTAs that may share one key range, i.e. the partial slots a cell needs.
+                              static_cast<unsigned long long>(kDecodeMaxParts));
+    // `splits` bounds the CTAs that may share one key range, i.e. the partial slots a cell needs; a cell can
+    // always be cut in two, so 1 reserves 2.
     unsigned long long parts = splits == 0 ? kNoAllocCellSplits / cells : (splits < 2 ? 2 : splits);
     if (parts > kDecodeMaxParts) parts = kDecodeMaxParts;
     if (parts < 2 || cells * parts > kNoAllocCellSplits)
@@ -706,25 +714,29 @@ extern "C" int itk_decode_attention_noalloc(const void* k_layer, const void* v_l
     int sm_count = 0;
     e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess || sm_count <= 0) sm_count = 148;
-    if (!g_noalloc_ptr[dev]) {
-        // One-time set-up for this device: resolve the array's device address and opt the kernel in to its
-        // dynamic shared memory size.  Neither allocates.
-        void* ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-        if (e != cudaSuccess || !ptr) {
-            if (error_text && error_text_len)
-                snprintf(error_text, error_text_len, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-            return 100;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(g_noalloc_mutex);
+        if (!g_noalloc_ptr[dev]) {
+            // One-time set-up for this device: resolve the array's device address and opt the kernel in to its
+            // dynamic shared memory size.  Neither allocates.
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+            if (e != cudaSuccess || !ptr) {
+                if (error_text && error_text_len)
+                    snprintf(error_text, error_text_len, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+                return 100;
+            }
+            e = configure_decode_f16();
+            if (e != cudaSuccess) {
+                if (error_text && error_text_len)
+                    snprintf(error_text, error_text_len, "kernel attribute setup failed: %s", cudaGetErrorString(e));
+                return 100;
+            }
+            g_noalloc_ptr[dev] = ptr;
         }
-        e = configure_decode_f16();
-        if (e != cudaSuccess) {
-            if (error_text && error_text_len)
-                snprintf(error_text, error_text_len, "kernel attribute setup failed: %s", cudaGetErrorString(e));
-            return 100;
-        }
-        g_noalloc_ptr[dev] = ptr;
+        base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
     }
-    unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
     AttnLaunch p{};

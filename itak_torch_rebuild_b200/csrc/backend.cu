@@ -94,7 +94,7 @@ struct itk_backend {
     float* acc_o = nullptr;  // fused-sum accumulators of the resident decode loop: [ticket_cells][8][head_dim], [..][8]
     float* acc_l = nullptr;
     unsigned int* acc_flag = nullptr;
-    bool fused_sum = true;   // ITK_DECODE_FUSED_SUM=0: cells shared by many CTAs are merged from the stored parts
+    bool fused_sum = true;   // option decode_fused_sum = 0: cells shared by many CTAs are merged from the stored parts
     size_t ticket_cells = 0;
     float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_out = nullptr;
     size_t stage_rows = 0;
@@ -105,10 +105,10 @@ struct itk_backend {
     itk_stats stats{};
     int sm_count = 148;
     int forced_splits = 0;
-    int forced_ctas = 0;         // ITK_DECODE_CTAS: persistent CTAs of the decode kernel (default 2 per SM)
-    bool separate_append = false;  // ITK_SEPARATE_APPEND=1: decode steps launch the append kernel separately
-    bool force_general = false;  // ITK_FORCE_GENERAL=1: multi-row launches take the CUDA-core kernel (A/B checks)
-    bool verify_tc = true;       // ITK_VERIFY_TC=0: multi-row launches take the mma.sync kernel instead of tcgen05
+    int forced_ctas = 0;         // option decode_ctas: persistent CTAs of the decode kernel (default 2 per SM)
+    bool separate_append = false;  // option separate_append = 1: decode steps launch the append kernel separately
+    bool force_general = false;  // option force_general = 1: multi-row launches take the CUDA-core kernel (A/B checks)
+    bool verify_tc = true;       // option verify_tc = 0: multi-row launches take the mma.sync kernel instead of tcgen05
     unsigned int* d_status = nullptr;  // device word kernels OR error bits into
     unsigned int* h_status = nullptr;  // pinned host copy read after a synchronisation
     bool status_pending = false;       // a kernel that can raise d_status was launched since the last check
@@ -124,9 +124,9 @@ struct itk_backend {
     unsigned char* gth_peer[itk::kMaxPeers] = {};
     uint32_t gth_world = 0, gth_rank = 0;
     uint64_t gth_bytes = 0;
-    bool gth_wait = true;  // ITK_GATHER_WAIT=0: do not check the peers' previous launch at kernel start
+    uint32_t gth_poll_limit = 200000;  // option gather_poll_limit: polls of a peer's arrival flag before giving up
     int res_prev_layer = -1;  // layer of the loop's previous launch on the stream, -1 = something else
-    bool use_pdl = true;      // ITK_PDL=0 turns programmatic dependent launch off
+    bool use_pdl = true;      // option pdl = 0 turns programmatic dependent launch off
     // attention preparation (per-head RMSNorm + rotary rotation), configured per layer
     struct LayerPrep {
         bool set = false;
@@ -217,6 +217,23 @@ uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uin
     return static_cast<uint32_t>(best);
 }
 
+// How a decode batch of `n_seqs` sequences with `cells_per_seq` (KV head x head chunk) cells each is cut into
+// launches so that the split scratch (kPartCellSplits partial slots) is never overrun: stream-K can cut any cell in
+// two, so every cell of a launch needs at least two slots.  *seqs_per_launch = sequences one launch may carry,
+// *parts_per_cell = partial slots each of its cells then owns (2..kDecodeMaxParts).  False when even one sequence
+// does not fit.
+bool decode_batch_limits(uint32_t n_seqs, uint32_t cells_per_seq, uint32_t* seqs_per_launch, uint32_t* parts_per_cell) {
+    if (n_seqs == 0 || cells_per_seq == 0 || 2ull * cells_per_seq > kPartCellSplits) return false;
+    uint64_t fit = kPartCellSplits / (2ull * cells_per_seq);
+    if (fit > static_cast<uint64_t>(itk::kMaxSeqsPerLaunch)) fit = itk::kMaxSeqsPerLaunch;
+    if (fit > n_seqs) fit = n_seqs;
+    uint64_t parts = kPartCellSplits / (fit * cells_per_seq);
+    if (parts > itk::kDecodeMaxParts) parts = itk::kDecodeMaxParts;
+    *seqs_per_launch = static_cast<uint32_t>(fit);
+    *parts_per_cell = static_cast<uint32_t>(parts);
+    return true;
+}
+
 // Event pair around one kernel launch while profiling is on; returns the pair's index or -1.
 long prof_begin(itk_backend* b, int tag) {
     if (b->prof_used + 2 > b->prof_events.size()) return -1;
@@ -295,6 +312,13 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
     while (per_launch > 1 && static_cast<uint64_t>(per_launch) * rows > 65535) per_launch >>= 1;
     if (static_cast<uint64_t>(rows) > 65535)
         return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(rows) + " rows exceed one launch's 65535-row limit");
+    if (decode) {
+        uint32_t fit = 0, parts = 0;
+        if (!decode_batch_limits(n, HY, &fit, &parts))
+            return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(HY) + " head cells per sequence exceed the split scratch of " +
+                                                 zu(kPartCellSplits) + " partial slots");
+        if (per_launch > fit) per_launch = fit;
+    }
     for (uint32_t at = 0; at < n; at += per_launch) {
         const uint32_t m = (n - at < per_launch) ? n - at : per_launch;
         AttnLaunch p{};
@@ -376,7 +400,7 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
 }
 
 // A decode step (one row per sequence, f16 cache, head_dim 64 or 128) lets the attention kernel store the new
-// row itself; ITK_SEPARATE_APPEND=1 keeps the two-launch form for A/B checks.
+// row itself; the option separate_append = 1 keeps the two-launch form for A/B checks.
 bool decode_fuses_append(const itk_backend* b, uint32_t rows) {
     return b->f16 && !b->separate_append && (b->cfg.head_dim % 8 == 0) && itk::decode_f16_supported(b->cfg.head_dim, rows);
 }
@@ -446,6 +470,11 @@ int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t*
     const bool fuse = decode_fuses_append(b, rows) || verify_fuses_append(b, rows);
     if (!fuse)
         if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
+    // The positions move only once the launch that stores the rows (the fused kernels) has been queued: a refused
+    // or failed launch leaves the slot where it was (the reference validates before any state moves,
+    // crates/cpu-compute/src/cpu.rs:558-581).
+    if (int rc = run_attention(b, layer, n_seqs, seqs.data(), rows, d_q, d_out, fuse ? d_k : nullptr, fuse ? d_v : nullptr))
+        return rc;
     for (uint32_t i = 0; i < n_seqs; ++i) {
         SlotState& st = b->slots[slots[i]];
         st.appended[layer] += rows;
@@ -453,7 +482,7 @@ int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t*
     }
     b->stats.rows_appended += static_cast<uint64_t>(n_seqs) * rows;
     b->stats.attention_calls += 1;
-    return run_attention(b, layer, n_seqs, seqs.data(), rows, d_q, d_out, fuse ? d_k : nullptr, fuse ? d_v : nullptr);
+    return ITK_OK;
 }
 
 int ensure_gather(itk_backend* b, size_t bytes) {
@@ -646,14 +675,6 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (e != cudaSuccess) return cuda_refuse(e, "initialisation");
     b->slots.resize(cfg->n_slots);
     for (uint32_t s = 0; s < cfg->n_slots; ++s) drop_slot(b, s);
-    if (const char* env = std::getenv("ITK_DECODE_SPLITS")) b->forced_splits = std::atoi(env);
-    if (const char* env = std::getenv("ITK_DECODE_CTAS")) b->forced_ctas = std::atoi(env);
-    if (const char* env = std::getenv("ITK_GATHER_WAIT")) b->gth_wait = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_PDL")) b->use_pdl = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_DECODE_FUSED_SUM")) b->fused_sum = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_SEPARATE_APPEND")) b->separate_append = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_FORCE_GENERAL")) b->force_general = std::atoi(env) != 0;
-    if (const char* env = std::getenv("ITK_VERIFY_TC")) b->verify_tc = std::atoi(env) != 0;
     *out = b;
     return ITK_OK;
 }
@@ -699,6 +720,32 @@ int itk_set_stream(itk_backend* b, void* cuda_stream) {
     if (!b) return ITK_ERR_INVALID_ARGUMENT;
     b->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : b->own_stream;
     return ITK_OK;
+}
+
+int itk_set_option(itk_backend* b, const char* name, int64_t value) {
+    if (!b || !name) return ITK_ERR_INVALID_ARGUMENT;
+    const std::string key(name);
+    if (b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: not while a resident loop is active");
+    auto flag = [&](bool* field) {
+        *field = value != 0;
+        return ITK_OK;
+    };
+    if (key == "decode_splits" || key == "decode_ctas") {
+        if (value < 0 || value > 4096) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: " + key + " must be 0..4096");
+        (key == "decode_splits" ? b->forced_splits : b->forced_ctas) = static_cast<int>(value);
+        return ITK_OK;
+    }
+    if (key == "pdl") return flag(&b->use_pdl);
+    if (key == "decode_fused_sum") return flag(&b->fused_sum);
+    if (key == "separate_append") return flag(&b->separate_append);
+    if (key == "force_general") return flag(&b->force_general);
+    if (key == "verify_tc") return flag(&b->verify_tc);
+    if (key == "gather_poll_limit") {
+        if (value < 1 || value > 100000000) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: gather_poll_limit must be 1..1e8");
+        b->gth_poll_limit = static_cast<uint32_t>(value);
+        return ITK_OK;
+    }
+    return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: unknown option '" + key + "'");
 }
 
 int itk_synchronize(itk_backend* b) {
@@ -749,6 +796,13 @@ int itk_decode_plan(const uint32_t* keys, uint32_t n_seqs, uint32_t cells_per_se
         o[5] = r.part;
     }
     return ITK_OK;
+}
+
+int itk_decode_batch_limits(uint32_t n_seqs, uint32_t cells_per_seq, uint32_t* seqs_per_launch, uint32_t* parts_per_cell,
+                            uint64_t* scratch_slots) {
+    if (!seqs_per_launch || !parts_per_cell || !scratch_slots) return ITK_ERR_INVALID_ARGUMENT;
+    *scratch_slots = kPartCellSplits;
+    return decode_batch_limits(n_seqs, cells_per_seq, seqs_per_launch, parts_per_cell) ? ITK_OK : ITK_ERR_CAPACITY;
 }
 
 int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, uint64_t max_steps) {
@@ -848,8 +902,8 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
                                 b->stream), "sequence-state upload");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
 #ifdef ITK_DECODE_TRACE
-    if (!g_trace && std::getenv("ITK_TRACE_DUMP")) {  // timeline build: allocate before any capture begins
-        void* ptr;
+    if (!g_trace) {  // timeline build: allocate before any capture begins; the caller reads it back through
+        void* ptr;   // itk_debug_trace_buffer
         uint64_t bytes;
         itk_debug_trace_buffer(&ptr, &bytes);
     }
@@ -929,7 +983,8 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
         p.gather.launches_per_step = b->cfg.n_layers;
         p.gather.launches_before = b->res_launches_in_step;
         p.gather.cells = p.n_seqs * b->cfg.kv_heads * b->gchunks;
-        p.gather.wait_prev = b->gth_wait ? 1u : 0u;
+        p.gather.wait_prev = 1u;
+        p.gather.poll_limit = b->gth_poll_limit;
     }
     // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
     // the same layer) the kernel waits first.
@@ -1036,20 +1091,6 @@ int itk_resident_end(itk_backend* b, uint64_t steps_done) {
     b->stats.rows_appended += steps_done * b->res_slots.size() * b->cfg.n_layers;
     b->stats.attention_calls += steps_done * b->cfg.n_layers;
     b->res_active = false;
-#ifdef ITK_DECODE_TRACE
-    if (const char* path = std::getenv("ITK_TRACE_DUMP")) {  // timeline build: the last step's stamps, raw u64
-        if (g_trace) {
-            cudaStreamSynchronize(b->stream);
-            std::vector<unsigned long long> host(64ull * 512 * 16);
-            cudaMemcpy(host.data(), g_trace, host.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-            const std::string name = std::string(path) + "." + std::to_string(b->cfg.device);
-            if (FILE* f = std::fopen(name.c_str(), "wb")) {
-                std::fwrite(host.data(), sizeof(unsigned long long), host.size(), f);
-                std::fclose(f);
-            }
-        }
-    }
-#endif
     return ITK_OK;
 }
 

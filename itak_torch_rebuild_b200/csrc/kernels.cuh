@@ -68,6 +68,7 @@ struct GatherTarget {
     uint32_t launches_before;            // decode launches of this step that precede this one
     uint32_t cells;                      // cells every rank delivers per launch
     uint32_t wait_prev;                  // 1 = before using its inputs, check that every peer's previous launch arrived
+    uint32_t poll_limit;                 // polls of one arrival flag before the wait gives up and records that
 };
 
 struct AttnLaunch {

@@ -16,10 +16,10 @@ def pattern_of(layer_window):
     return [orc.LayerKind.Windowed(w) if w else orc.GLOBAL for w in layer_window]
 
 
-def make_pair(layer_window, hq, hkv, d, *, dtype=KvDtype.F16, n_slots=1, max_context=1024, chunk_cap=8):
+def make_pair(layer_window, hq, hkv, d, *, dtype=KvDtype.F16, n_slots=1, max_context=1024, chunk_cap=8, options=None):
     """(CudaCompute, [oracle KvCache per slot]) over the same geometry."""
     gpu = CudaCompute(len(layer_window), hq, hkv, d, n_slots=n_slots, max_context=max_context, chunk_cap=chunk_cap,
-                      kv_dtype=dtype, layer_window=list(layer_window))
+                      kv_dtype=dtype, layer_window=list(layer_window), options=options)
     refs = [orc.KvCache(pattern_of(layer_window), hkv, d) for _ in range(n_slots)]
     return gpu, refs
 

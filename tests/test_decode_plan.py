@@ -98,3 +98,32 @@ def test_refusals():
     assert lib.itk_decode_plan((C.c_uint32 * 1)(0), 1, 1, 1, 2, C.byref(aligned), runs) == _lib.ERR_INVALID_ARGUMENT
     assert lib.itk_decode_plan((C.c_uint32 * 1)(5), 0, 1, 1, 2, C.byref(aligned), runs) == _lib.ERR_INVALID_ARGUMENT
     assert lib.itk_decode_plan((C.c_uint32 * 1)(5), 1, 1, 0, 2, C.byref(aligned), runs) == _lib.ERR_INVALID_ARGUMENT
+
+
+def batch_limits(n_seqs, cells_per_seq):
+    lib = _lib.load()
+    per, parts, slots = C.c_uint32(), C.c_uint32(), C.c_uint64()
+    rc = lib.itk_decode_batch_limits(n_seqs, cells_per_seq, C.byref(per), C.byref(parts), C.byref(slots))
+    return rc, per.value, parts.value, slots.value
+
+
+@pytest.mark.parametrize("n_seqs,cells_per_seq", [(8, 8), (64, 8), (50, 96), (64, 128), (64, 2 * 37), (1, 4736), (3, 4000)])
+def test_large_decode_batches_never_overrun_the_split_scratch(n_seqs, cells_per_seq):
+    """A batch whose (sequence, head) cells exceed half the scratch goes out as several launches: every launch keeps
+    cells x parts within the scratch and every cell keeps the two slots a stream-K cut can need (50 sequences of 96
+    MHA heads, or 64 of 128 head cells, used to leave one slot per cell and write past the end)."""
+    rc, per, parts, slots = batch_limits(n_seqs, cells_per_seq)
+    assert rc == _lib.OK
+    assert 1 <= per <= min(n_seqs, 64)
+    assert 2 <= parts <= 64
+    assert per * cells_per_seq * parts <= slots
+    # and the plan the launcher derives for such a launch never numbers a part beyond that bound
+    keys = [777] * per
+    if per * cells_per_seq <= 4096:
+        _, runs = plan(keys, cells_per_seq, 296, parts)
+        assert runs[:, 4].max() <= max(parts, 2)
+
+
+def test_a_sequence_whose_cells_do_not_fit_twice_is_refused():
+    rc, _, _, slots = batch_limits(1, 4737)
+    assert rc == _lib.ERR_CAPACITY and slots == 9472

@@ -3,7 +3,6 @@ geometries, and sweeps over context length, KV split count, head grouping and ca
 
 Tolerance (stated by the task): max-abs error <= 1e-4 (f32 cache) or 2e-3 (f16 cache) of the output norm."""
 import ctypes as C
-import os
 
 import numpy as np
 import pytest
@@ -75,15 +74,12 @@ def seeded_case(dtype, hq, hkv, d, n, seed, layer_window=(0,), ctas=None, separa
     """Append n seeded N(0,1) rows, then decode steps through the backend's attention call; the outputs and,
     afterwards, the cache contents (the step's rows are stored by the attention launch itself on the f16
     tensor-core path) are compared with the oracle."""
+    options = {}
     if ctas is not None:
-        os.environ["ITK_DECODE_CTAS"] = str(ctas)
+        options["decode_ctas"] = ctas
     if separate_append:
-        os.environ["ITK_SEPARATE_APPEND"] = "1"
-    try:
-        gpu, (ref,) = make_pair(list(layer_window), hq, hkv, d, dtype=dtype, max_context=n + 8, chunk_cap=1)
-    finally:
-        os.environ.pop("ITK_DECODE_CTAS", None)
-        os.environ.pop("ITK_SEPARATE_APPEND", None)
+        options["separate_append"] = 1
+    gpu, (ref,) = make_pair(list(layer_window), hq, hkv, d, dtype=dtype, max_context=n + 8, chunk_cap=1, options=options)
     rng = np.random.default_rng(seed)
     worst = 0.0
     for layer in range(len(layer_window)):

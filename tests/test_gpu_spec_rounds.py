@@ -1,7 +1,6 @@
 """The speculative (DFlash-style) path end to end on the device: shared prefix restored into sessions, rounds
 of append 7 rows + tensor-core causal verify attention + truncate to the accepted length
 (crates/itak-spec/src/session.rs:663-747: checkpoint -> block forward -> rewind(base + 1 + accepted) -> release)."""
-import os
 
 import numpy as np
 import pytest
@@ -80,13 +79,9 @@ def test_verify_kernel_agrees_with_the_cuda_core_kernel():
     k = rng.standard_normal((rows, hkv * d)).astype(np.float32)
     v = rng.standard_normal((rows, hkv * d)).astype(np.float32)
     outs = []
-    for force in ("0", "1"):
-        os.environ["ITK_FORCE_GENERAL"] = force
-        try:
-            gpu = CudaCompute(2, hq, hkv, d, n_slots=1, max_context=600, chunk_cap=rows, kv_dtype=KvDtype.F16,
-                              layer_window=[0, 128])
-        finally:
-            os.environ.pop("ITK_FORCE_GENERAL", None)
+    for force in (0, 1):
+        gpu = CudaCompute(2, hq, hkv, d, n_slots=1, max_context=600, chunk_cap=rows, kv_dtype=KvDtype.F16,
+                          layer_window=[0, 128], options={"force_general": force})
         from itak_torch_rebuild_b200 import PositionCache
 
         pos = PositionCache()

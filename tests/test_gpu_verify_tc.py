@@ -1,7 +1,6 @@
 """The tcgen05 (tensor-memory) multi-row attention kernel against the oracle's multi-query gqa_attention
 (crates/attention/src/attention.rs:160-213) and against the mma.sync kernel it replaces: every pair-block
 width (replicated 4x, 2x, not at all, several blocks), key splits, partial tiles, ring wrap and windows."""
-import os
 
 import numpy as np
 import pytest
@@ -21,15 +20,8 @@ TIGHT = 2e-5
 
 def build(layer_window, hq, hkv, n0, rows, *, env=None, n_slots=1, seed=0):
     """Backend + oracle caches holding n0 seeded rows per layer; windowed layers are fed chunk by chunk."""
-    env = env or {}
-    for key, val in env.items():
-        os.environ[key] = val
-    try:
-        gpu, refs = make_pair(list(layer_window), hq, hkv, D, dtype=DTYPE, n_slots=n_slots, max_context=n0 + 4 * rows + 8,
-                              chunk_cap=rows)
-    finally:
-        for key in env:
-            os.environ.pop(key, None)
+    gpu, refs = make_pair(list(layer_window), hq, hkv, D, dtype=DTYPE, n_slots=n_slots, max_context=n0 + 4 * rows + 8,
+                          chunk_cap=rows, options=env)
     rng = np.random.default_rng(seed)
     for slot in range(n_slots):
         for layer, w in enumerate(layer_window):
@@ -100,7 +92,7 @@ def test_every_tail_length(n0):
 def test_every_key_split(splits):
     """Forced split counts, including more splits than tiles (empty CTAs take part in the merge)."""
     n0 = 1500
-    gpu, refs = build([0], 32, 8, n0, 7, env={"ITK_DECODE_SPLITS": str(splits)}, seed=1)
+    gpu, refs = build([0], 32, 8, n0, 7, env={"decode_splits": splits}, seed=1)
     worst, _ = run_blocks(gpu, refs, [0], 32, 8, n0, 7, blocks=2, seed=6)
     assert worst < TIGHT, worst
     assert gpu.stats()["last_splits"] == min(splits, (n0 + 14 + 63) // 64)
@@ -151,12 +143,9 @@ def test_agrees_with_the_mma_sync_kernel_on_batched_sessions():
     k = rng.standard_normal((len(lens), rows, hkv * D)).astype(np.float32)
     v = rng.standard_normal((len(lens), rows, hkv * D)).astype(np.float32)
     outs = []
-    for flag in ("1", "0"):
-        os.environ["ITK_VERIFY_TC"] = flag
-        try:
-            gpu = CudaCompute(1, hq, hkv, D, n_slots=len(lens), max_context=2100, chunk_cap=rows, kv_dtype=DTYPE)
-        finally:
-            os.environ.pop("ITK_VERIFY_TC", None)
+    for flag in (1, 0):
+        gpu = CudaCompute(1, hq, hkv, D, n_slots=len(lens), max_context=2100, chunk_cap=rows, kv_dtype=DTYPE,
+                          options={"verify_tc": flag})
         for slot, (k0, v0) in enumerate(data):
             gpu.append_rows(0, k0, v0, 0, slot=slot)
         outs.append(gpu.attention_batch(0, list(range(len(lens))), lens, rows, q, k, v))
