@@ -144,7 +144,10 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * in L2, default 1), "separate_append" (decode steps launch the append kernel separately, default 0),
  * "force_general" (multi-row calls take the CUDA-core kernel, default 0), "verify_tc" (multi-row calls take the
  * tcgen05 kernel, default 1), "gather_poll_limit" (polls of a peer's arrival flag before the fused gather's wait
- * gives up, default 200000).  Unknown names and out-of-range values are refused; not allowed inside a resident loop. */
+ * gives up, default 200000), "decode_lanes" (two-lane schedule of the gathering loop: 0 never, 1 when a launch is
+ * short enough to gain, 2 whenever possible; default 1), "decode_lane_stagger" (the second lane of a step's first
+ * launch starts behind the first, default 1).  Unknown names and out-of-range values are refused; not allowed inside
+ * a resident loop. */
 int itk_set_option(itk_backend* b, const char* name, int64_t value);
 int itk_synchronize(itk_backend* b);
 int itk_get_stats(const itk_backend* b, itk_stats* out);
@@ -179,6 +182,16 @@ int itk_attention(itk_backend* b, uint32_t slot, uint32_t layer, const float* q,
 int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
                         const uint64_t* positions, uint32_t rows, const float* q, const float* k, const float* v,
                         float* out);
+
+/* The attention step of EVERY layer of one forward in one call, for a caller that holds all layers' projections
+ * on the host (a benchmark of the path alone, a replay of recorded activations): host q [layers][n_seqs][rows][q_heads*D],
+ * k, v [layers][n_seqs][rows][kv_heads*D], out like q; every slot must sit at positions[i] on every layer.  The
+ * backend pipelines the layers over three streams - layer l's rows upload while layer l-1 computes and layer l-2's
+ * result downloads - and returns after the last result is in `out`.  Same refusals as itk_attention_batch, all
+ * layers validated before anything is queued.  The first call allocates the per-layer staging.  No counterpart in
+ * the reference, whose forward calls Compute::attention layer by layer (crates/muse-glimmer/src/model.rs:452-462). */
+int itk_attention_layers_host(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, const uint64_t* positions,
+                              uint32_t rows, const float* q, const float* k, const float* v, float* out);
 
 /* As itk_attention_batch with q, k, v, out resident in device memory; returns
  * once the work is queued on the backend's stream. */
@@ -251,13 +264,23 @@ int itk_resident_end(itk_backend* b, uint64_t steps_done);
  * host channel) and open each other's; inside the replayable loop itk_resident_layer_gather then behaves like
  * itk_resident_layer, except that the CTA finishing a (sequence, head) cell stores its rows - plain stores to
  * peer-mapped memory over NVLink - at `gather_offset_bytes` of EVERY rank's buffer (the caller gives each rank
- * and layer its own offset), and counts the cell on every rank's flag array.  Before a kernel of the loop uses
- * its inputs it checks, with a bounded wait, that all ranks' cells of the previous launch have arrived
- * (itk_gather_status reports a wait that ran out).  All ranks must call itk_gather_reset, then synchronise with
+ * and layer its own offset), and counts the cell on every rank's flag array.  A short launch runs as two lanes -
+ * the batch cut in two halves of about equal work, half of the grid's CTAs each, separate arrival counters - which
+ * the backend keeps out of phase, so that one half's outputs cross NVLink while the other half streams its cache (a
+ * layer's inputs for a sequence depend on the previous layer's gathered outputs of that sequence only).  Before a
+ * kernel of the loop uses its inputs it checks, with a bounded wait, that all ranks' cells of the previous launch
+ * (of its lane) have arrived
+ * (itk_gather_status reports a wait that ran out: bit 0 of *error_bits; the kernel then carries on, its own outputs
+ * do not depend on the peers' rows).  All ranks must call itk_gather_reset, then synchronise with
  * each other, before itk_resident_begin; a step of the loop must launch every layer exactly once. */
 int itk_gather_create(itk_backend* b, uint32_t world, uint32_t rank, uint64_t data_bytes, void** local_data,
                       uint8_t* handle64);
 int itk_gather_open(itk_backend* b, uint32_t peer_rank, const uint8_t* handle64);
+/* As itk_gather_open for a peer whose buffer this process can already address - another backend of the same
+ * process (one process driving several GPUs with peer access enabled), or memory mapped by the caller's own
+ * symmetric-memory allocator: `peer_local_data` is the pointer itk_gather_create returned as *local_data on that
+ * peer.  The mapping stays the caller's. */
+int itk_gather_attach(itk_backend* b, uint32_t peer_rank, void* peer_local_data);
 int itk_gather_reset(itk_backend* b);
 int itk_gather_status(itk_backend* b, uint32_t* error_bits);
 int itk_resident_layer_gather(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
@@ -378,12 +401,26 @@ int itk_snapshot_from_host_f32(itk_backend* b, uint64_t token_count, const uint6
  * protocol: with out == NULL only *size is set. */
 int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* snap, const char* model_fingerprint, uint8_t* out,
                          size_t capacity, size_t* size);
+/* The same with the format version chosen.  Version 1 is the reference's (f32 rows, what itk_snapshot_to_itkv
+ * writes).  Version 2 is this library's extension for f16 caches, which the reference refuses to snapshot
+ * (crates/wgpu-compute/src/session.rs:383-398): one more header field - a u32 element type directly after the
+ * version, 0 = f32, 1 = IEEE half - and the rows stored in that type, so an f16 cache's prefix takes half the bytes
+ * and its bit patterns survive a round trip untouched.  itk_snapshot_from_itkv reads both (half rows bound for an
+ * f32 cache are widened exactly; f32 rows bound for an f16 cache are rounded as an append rounds). */
+int itk_snapshot_to_itkv_version(itk_backend* b, const itk_snapshot* snap, const char* model_fingerprint,
+                                 uint32_t version, uint8_t* out, size_t capacity, size_t* size);
 /* KvSnapshot::from_bytes followed by restore_checked's trust checks (snapshot.rs:425-540, 345-371): strict
- * decode (bad magic, unknown version, truncation, layer count beyond the buffer, overflowing products, trailing
- * bytes, checksum, self-consistency - each a named refusal), then the backend's geometry and, when
+ * decode (bad magic, unknown version or element type, truncation, layer count beyond the buffer, overflowing
+ * products, trailing bytes, checksum, self-consistency - each a named refusal), then the backend's geometry and, when
  * expected_fingerprint is not NULL, the model fingerprint.  Rows are cast to the cache's element type. */
 int itk_snapshot_from_itkv(itk_backend* b, const uint8_t* bytes, size_t n, const char* expected_fingerprint,
                            itk_snapshot** out);
+
+/* The strict decode alone (KvSnapshot::from_bytes + validate, crates/itak-kv/src/snapshot.rs:187-236, 425-540), host
+ * code only: vets ITKV bytes of either format version without a backend or a device.  Returns ITK_OK and the
+ * header's version, token count and bytes per stored element, or the refusal's code with its text in `why`. */
+int itk_itkv_check(const uint8_t* bytes, size_t n, uint32_t* version, uint64_t* token_count, uint32_t* elem_bytes,
+                   char* why, size_t why_len);
 
 /* ---- for callers that cannot allocate ------------------------------------------------ */
 

@@ -110,6 +110,7 @@ SIGNATURES = {
     "itk_get_stats": (C.c_int, [_vp, C.POINTER(Stats)]),
     "itk_attention": (C.c_int, [_vp, _u32, _u32, _vp, _sz, _vp, _sz, _vp, _sz, _u64, _vp]),
     "itk_attention_batch": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
+    "itk_attention_layers_host": (C.c_int, [_vp, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_attention_batch_device": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
     "itk_layer_prep_set": (C.c_int, [_vp, _u32, C.POINTER(PrepConfig)]),
     "itk_attention_batch_prep": (C.c_int, [_vp, _u32, _u32, _u32p, _u64p, _u32, _vp, _vp, _vp, _vp]),
@@ -122,6 +123,7 @@ SIGNATURES = {
     "itk_resident_end": (C.c_int, [_vp, _u64]),
     "itk_gather_create": (C.c_int, [_vp, _u32, _u32, _u64, C.POINTER(_vp), _vp]),
     "itk_gather_open": (C.c_int, [_vp, _u32, _vp]),
+    "itk_gather_attach": (C.c_int, [_vp, _u32, _vp]),
     "itk_gather_reset": (C.c_int, [_vp]),
     "itk_gather_status": (C.c_int, [_vp, _u32p]),
     "itk_resident_layer_gather": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _u64]),
@@ -148,7 +150,9 @@ SIGNATURES = {
     "itk_snapshot_layer_to_host": (C.c_int, [_vp, _vp, _u32, _vp, _vp, _u64p, _u64p]),
     "itk_snapshot_from_host_f32": (C.c_int, [_vp, _u64, _u64p, _u64p, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
     "itk_snapshot_to_itkv": (C.c_int, [_vp, _vp, C.c_char_p, _vp, _sz, C.POINTER(_sz)]),
+    "itk_snapshot_to_itkv_version": (C.c_int, [_vp, _vp, C.c_char_p, _u32, _vp, _sz, C.POINTER(_sz)]),
     "itk_snapshot_from_itkv": (C.c_int, [_vp, C.c_char_p, _sz, C.c_char_p, C.POINTER(_vp)]),
+    "itk_itkv_check": (C.c_int, [C.c_char_p, _sz, _u32p, _u64p, _u32p, C.c_char_p, _sz]),
     "itk_draft_attention": (C.c_int, [_vp, _vp, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
                                       _u32, _u32, C.c_float, _vp, _vp, C.c_char_p, _sz]),
     "itk_prefix_store_open": (C.c_int, [C.c_char_p, _u64, C.POINTER(_vp)]),

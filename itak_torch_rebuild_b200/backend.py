@@ -92,13 +92,15 @@ class DeviceSnapshot:
     def payload_bytes(self) -> int:
         return _lib.load().itk_snapshot_payload_bytes(self._h)
 
-    def to_itkv(self, model_fingerprint: str) -> bytes:
-        """The snapshot in the reference's versioned ``ITKV`` byte format (f32 rows, FNV-1a-64 checksum)."""
+    def to_itkv(self, model_fingerprint: str, version: int = 1) -> bytes:
+        """The snapshot in the versioned ``ITKV`` byte format with its FNV-1a-64 checksum: version 1 is the
+        reference's (f32 rows), version 2 stores the rows in the cache's own element type (half the bytes for f16)."""
         b = self._owner
         size = C.c_size_t()
-        b._check(b._lib.itk_snapshot_to_itkv(b._h, self._h, model_fingerprint.encode(), None, 0, C.byref(size)))
+        fp = model_fingerprint.encode()
+        b._check(b._lib.itk_snapshot_to_itkv_version(b._h, self._h, fp, version, None, 0, C.byref(size)))
         buf = (C.c_uint8 * size.value)()
-        b._check(b._lib.itk_snapshot_to_itkv(b._h, self._h, model_fingerprint.encode(), buf, size.value, C.byref(size)))
+        b._check(b._lib.itk_snapshot_to_itkv_version(b._h, self._h, fp, version, buf, size.value, C.byref(size)))
         return bytes(buf)
 
     def layer(self, layer: int):
@@ -225,6 +227,22 @@ class CudaCompute:
         self._check(fn(self._h, layer, n, slots_c, positions_c, rows, C.c_void_p(q_ptr), C.c_void_p(k_ptr),
                        C.c_void_p(v_ptr), C.c_void_p(out_ptr)))
 
+    def attention_layers_host_ptrs(self, slots_c, positions_c, n: int, rows: int, q_ptr: int, k_ptr: int, v_ptr: int,
+                                   out_ptr: int):
+        """Every layer's attention step of one forward from host buffers ``[layers][n][rows][...]`` in one call;
+        uploads, kernels and downloads of consecutive layers overlap.  Raw-pointer form."""
+        self._check(self._lib.itk_attention_layers_host(self._h, n, slots_c, positions_c, rows, C.c_void_p(q_ptr),
+                                                        C.c_void_p(k_ptr), C.c_void_p(v_ptr), C.c_void_p(out_ptr)))
+
+    def attention_layers_host(self, slots: Sequence[int], positions: Sequence[int], rows: int, q, k, v) -> np.ndarray:
+        n = len(slots)
+        q, k, v = _host_f32(q), _host_f32(k), _host_f32(v)
+        out = np.empty(self.n_layers * n * rows * self.q_width, dtype=np.float32)
+        sl = (C.c_uint32 * n)(*slots)
+        ps = (C.c_uint64 * n)(*positions)
+        self.attention_layers_host_ptrs(sl, ps, n, rows, q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data)
+        return out
+
     # -- attention preparation on the device (RMSNorm + RoPE ahead of the append) -----------------------------
     def set_layer_prep(self, layer: int, *, q_norm_weight=None, k_norm_weight=None, norm_eps: float = 1e-6,
                        rope_base: Optional[float] = None, rotary_dim: Optional[int] = None, pairing: int = 0):
@@ -301,6 +319,11 @@ class CudaCompute:
     def gather_open(self, peer_rank: int, handle: bytes):
         buf = (C.c_uint8 * 64).from_buffer_copy(handle)
         self._check(self._lib.itk_gather_open(self._h, peer_rank, buf))
+
+    def gather_attach(self, peer_rank: int, peer_data_ptr: int):
+        """Open a peer whose gather buffer this process already addresses (``peer_data_ptr`` = what ``gather_create``
+        returned on that peer)."""
+        self._check(self._lib.itk_gather_attach(self._h, peer_rank, C.c_void_p(peer_data_ptr)))
 
     def gather_reset(self):
         self._check(self._lib.itk_gather_reset(self._h))

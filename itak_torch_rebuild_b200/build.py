@@ -72,5 +72,53 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return SO_PATH
 
 
+ASAN_PATH = os.path.join(LIB_DIR, "libitak_host_asan.so")
+HOST_ONLY_SOURCES = ["prefix_store.cu"]  # no kernel, no CUDA call: compiles as plain C++
+
+
+def sanitizer_compiler():
+    """The first C++ compiler among the system g++, the one on PATH and $CXX that can link the sanitizer runtimes
+    (a toolchain without libasan fails at link time), or None."""
+    import tempfile
+
+    seen = []
+    for cand in ("/usr/bin/g++", shutil.which("g++"), os.environ.get("CXX")):
+        if not cand or cand in seen or not os.path.exists(cand):
+            continue
+        seen.append(cand)
+        with tempfile.TemporaryDirectory() as tmp:
+            src = os.path.join(tmp, "probe.cpp")
+            with open(src, "w") as f:
+                f.write("int main() { return 0; }\n")
+            res = subprocess.run([cand, "-fsanitize=address,undefined", src, "-o", os.path.join(tmp, "probe")],
+                                 capture_output=True, text=True)
+            if res.returncode == 0:
+                return cand
+    return None
+
+
+def build_sanitized(force: bool = False) -> str:
+    """The host-only part of the library (the prefix store and the ITKV decoder, which parse untrusted bytes) built
+    with g++ under AddressSanitizer and UndefinedBehaviorSanitizer, for the CPU tests that feed it forged input."""
+    srcs = [os.path.join(CSRC, f) for f in HOST_ONLY_SOURCES]
+    deps = srcs + glob.glob(os.path.join(CSRC, "*.hpp")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    if not force and os.path.exists(ASAN_PATH) and all(os.path.getmtime(d) <= os.path.getmtime(ASAN_PATH) for d in deps):
+        return ASAN_PATH
+    os.makedirs(LIB_DIR, exist_ok=True)
+    cxx = sanitizer_compiler()
+    if cxx is None:
+        raise RuntimeError("no C++ compiler here links -fsanitize=address,undefined")
+    cmd = [cxx, "-std=c++17", "-O1", "-g", "-fPIC", "-shared", "-fsanitize=address,undefined",
+           "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer"]
+    for src in srcs:
+        cmd += ["-x", "c++", src]
+    cmd += ["-x", "none", "-o", ASAN_PATH]  # "-x c++" must not reach the sanitizer runtimes the driver appends
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("sanitized host build failed")
+    return ASAN_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

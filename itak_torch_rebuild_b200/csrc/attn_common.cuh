@@ -77,7 +77,7 @@ __device__ __forceinline__ void store_out4(const AttnLaunch& p, size_t off4, flo
     for (uint32_t j = 0; j < p.gather.n_peers; ++j) reinterpret_cast<float4*>(p.gather.peer_out[j])[off4] = v;
 }
 // After a cell's output went out: make it visible system-wide, then count it on every rank.
-__device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p) {
+__device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p, uint32_t lane = 0) {
     if (p.gather.n_peers == 0) return;
     // The CTA's stores are ordered before the barrier, and one thread's system-scope fence after it is cumulative
     // over them (the grid-barrier idiom): one fence per CTA instead of one per thread.  Then a reduction per peer
@@ -87,7 +87,7 @@ __device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p) {
         __threadfence_system();
         ITK_TRACE(p, 15);  // (timeline build) the system-scope fence has returned
         for (uint32_t j = 0; j < p.gather.n_peers; ++j)
-            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[j] + p.gather.my_rank) : "memory");
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[j] + lane * kMaxPeers + p.gather.my_rank) : "memory");
     }
 }
 
@@ -162,11 +162,12 @@ __device__ __forceinline__ void finish_weights(const float* all_ml, uint32_t n_p
 // With AttnLaunch::acc_o set, a cell shared by more than kFusedSumMinParts CTAs
 // is summed in L2 instead (see below) and the last arrival reads one
 // accumulator rather than every part.
-// The ticket counter (and the accumulator) is left at zero for the next launch.
+// The ticket counter (and the accumulator) is left at zero for the next launch, before the cell is announced.
 template <int THREADS, int MAXP>
 __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t n_parts,
                                             uint32_t part, uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
-                                            const float* fm, const float* fl, int* s_flag, float* wscratch) {
+                                            const float* fm, const float* fl, int* s_flag, float* wscratch,
+                                            uint32_t lane = 0) {
     const uint32_t tid = threadIdx.x;
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
     const size_t out_off = (static_cast<size_t>(unit) * p.q_heads + head0) * D;  // element offset of the cell's rows
@@ -175,7 +176,7 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
             const uint32_t h = idx / D;
             store_out(p, out_off + idx, fo[idx] / fl[h]);
         }
-        signal_cell_delivered(p);
+        signal_cell_delivered(p, lane);
         return;
     }
     const size_t cell = static_cast<size_t>(unit) * HY + hy;
@@ -247,8 +248,10 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
                 const float i0 = 1.f / l0, i1 = 1.f / l1;
                 if (c0 < cols) store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
                 if (c1 < cols) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
-                signal_cell_delivered(p);
+                // the counter is back at zero BEFORE the cell is announced: a launch that orders itself by the
+                // arrival counters alone may take its first ticket the moment it sees the announcement
                 if (tid == 0) p.tickets[cell] = 0u;
+                signal_cell_delivered(p, lane);
                 return;
             }
         }
@@ -315,8 +318,8 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
             store_out(p, out_off + idx, acc * inv_l[h]);
         }
     }
-    signal_cell_delivered(p);
-    if (tid == 0) p.tickets[cell] = 0u;
+    if (tid == 0) p.tickets[cell] = 0u;  // before the announcement, as above
+    signal_cell_delivered(p, lane);
 }
 
 }  // namespace itk

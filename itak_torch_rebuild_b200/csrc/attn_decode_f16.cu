@@ -125,38 +125,51 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     const bool fused = p.k_new != nullptr;
 
     ITK_TRACE(p, 0);
-    if (p.pdl != 0) pdl_launch_dependents();
+    // A launch that must wait for its predecessor before anything else (the first of a step, behind the position
+    // advance) lets its own dependents start only after that wait: they may then rely on what it waited for.
     if (p.pdl == 1) pdl_wait();
+    if (p.pdl != 0) pdl_launch_dependents();
     uint32_t* abase = cum + (kMaxSeqsPerLaunch + 4);
-    uint32_t* sn = abase + (kMaxSeqsPerLaunch + 4);  // visible keys per sequence
-    uint32_t* ss0 = sn + kMaxSeqsPerLaunch;          // storage row of its first visible key
-    uint32_t* sslot = ss0 + kMaxSeqsPerLaunch;
-    uint32_t* mode = sslot + kMaxSeqsPerLaunch;      // [0] 1 = cell-aligned plan
-    if (static_cast<uint32_t>(tid) < p.n_seqs) {     // one global read per sequence, all in flight together
+    uint32_t* sn_all = abase + (kMaxSeqsPerLaunch + 4);  // visible keys per sequence
+    uint32_t* ss0_all = sn_all + kMaxSeqsPerLaunch;      // storage row of its first visible key
+    uint32_t* sslot_all = ss0_all + kMaxSeqsPerLaunch;
+    uint32_t* mode = sslot_all + kMaxSeqsPerLaunch;      // [0] 1 = cell-aligned plan
+    if (static_cast<uint32_t>(tid) < p.n_seqs) {         // one global read per sequence, all in flight together
         const SeqDesc sd = seq_of(p, tid);
-        sn[tid] = sd.kv_hi - sd.kv_lo;
-        ss0[tid] = sd.kv_lo % ring;
-        sslot[tid] = sd.slot;
+        sn_all[tid] = sd.kv_hi - sd.kv_lo;
+        ss0_all[tid] = sd.kv_lo % ring;
+        sslot_all[tid] = sd.slot;
     }
+    // Two lanes: the first half of the grid walks sequences [0, lane_split), the second half the rest; each half
+    // plans its own sequences with its own CTAs, and everything below indexes the lane's sequences from zero.
+    const bool two_lanes = p.gather.lanes == 2;
+    const uint32_t G = two_lanes ? gridDim.x / 2 : gridDim.x;            // CTAs of this CTA's lane
+    const uint32_t glane = (two_lanes && blockIdx.x >= G) ? 1u : 0u;  // which lane this CTA serves
+    const uint32_t cta = blockIdx.x - glane * G;                          // this CTA's number inside its lane
+    const uint32_t seq_base = glane ? p.gather.lane_split : 0u;           // lane's first sequence in the launch
+    const uint32_t n_seqs = two_lanes ? (glane ? p.n_seqs - p.gather.lane_split : p.gather.lane_split) : p.n_seqs;
+    const uint32_t* sn = sn_all + seq_base;
+    const uint32_t* ss0 = ss0_all + seq_base;
+    const uint32_t* sslot = sslot_all + seq_base;
     __syncthreads();
     if (tid == 0) {
-        // cum[s] = tiles of all cells before sequence s
+        // cum[s] = tiles of all cells before (lane-local) sequence s
         uint32_t c = 0;
-        for (uint32_t s = 0; s < p.n_seqs; ++s) {
+        for (uint32_t s = 0; s < n_seqs; ++s) {
             cum[s] = c;
             c += (sn[s] + kTileKeys - 1) / kTileKeys * HY;
         }
-        cum[p.n_seqs] = c;
+        cum[n_seqs] = c;
         // The cell-aligned plan, if it costs at most a sixteenth more tiles per CTA than equal runs would.
-        const uint32_t G = gridDim.x, total = c;
+        const uint32_t total = c;
         const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
         uint32_t worst;
-        mode[0] = decode_aligned_plan(sn, p.n_seqs, HY, G, total, per, p.splits, abase, &worst) ? 1u : 0u;
+        mode[0] = decode_aligned_plan(sn, n_seqs, HY, G, total, per, p.splits, abase, &worst) ? 1u : 0u;
     }
     __syncthreads();
-    const uint32_t total = cum[p.n_seqs];
+    const uint32_t total = cum[n_seqs];
     const bool aligned = mode[0] != 0u;
-    const uint32_t per = p.seq_dev ? (total + gridDim.x - 1) / gridDim.x : p.tiles_per_cta;
+    const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
 
     auto enter_seq = [&](TileCursor& c) {
         c.n = sn[c.seq];
@@ -169,12 +182,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             c.tile = 0;
             if (++c.hy == HY) {
                 c.hy = 0;
-                if (++c.seq < p.n_seqs) enter_seq(c);
+                if (++c.seq < n_seqs) enter_seq(c);
             }
         }
     };
     TileCursor lc;  // load cursor, runs STAGES - 1 tiles ahead of the compute cursor
-    const DecodeRun my = decode_cta_run(aligned, blockIdx.x, sn, cum, abase, p.n_seqs, HY, per);
+    const DecodeRun my = decode_cta_run(aligned, cta, sn, cum, abase, n_seqs, HY, per);
     const uint32_t ntiles = my.ntiles;
     const uint32_t al_parts = my.parts, al_part = my.part;  // aligned plan: CTAs sharing this CTA's cell, and which
     if (ntiles != 0) {
@@ -184,7 +197,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         lc.tile = my.tile;
     }
     if (ntiles == 0) {
-        if (p.pdl == 2) pdl_wait();
+        if (p.pdl >= 2) pdl_wait();
         return;
     }
     ITK_TRACE(p, 1);
@@ -238,13 +251,24 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     // A layer's inputs exist only once every rank's heads of the previous layer have been gathered: check that the
     // peers' previous launch has arrived here.  The wait is bounded; if it runs out the kernel records that and
     // carries on (its own arithmetic does not depend on the gathered data).
+    // With two lanes the counters are the lane's own, and they also order everything this launch shares with the
+    // previous one (split scratch, tickets, accumulators of the lane's cells): the rank's own counter is among those
+    // polled, and a cell is announced only after its merge has read the scratch and reset its ticket.
     if (p.gather.n_peers != 0 && p.gather.wait_prev != 0) {
-        if (static_cast<uint32_t>(tid) < p.gather.n_peers) {  // one polling thread per source rank
+        const uint32_t pollers = p.gather.n_peers + ((p.gather.stagger != 0 && glane == 1) ? 1u : 0u);
+        if (static_cast<uint32_t>(tid) < pollers) {  // one polling thread per source rank
             const uint32_t steps_done = seq_of(p, 0).q_pos0 - *p.gather.base_pos;
-            const uint32_t target = (steps_done * p.gather.launches_per_step + p.gather.launches_before) * p.gather.cells;
+            const uint32_t launches_done = steps_done * p.gather.launches_per_step + p.gather.launches_before;
+            const unsigned int* arrived = p.gather.my_flags + glane * kMaxPeers + tid;
+            uint32_t target = launches_done * p.gather.lane_cells[glane];
+            if (static_cast<uint32_t>(tid) == p.gather.n_peers) {
+                // lane 1 of a step's first launch: hold back until this rank's lane 0 has delivered THIS launch
+                arrived = p.gather.my_flags + p.gather.my_rank;
+                target = (launches_done + 1) * p.gather.lane_cells[0];
+            }
             uint32_t seen = 0, spins = 0;
             for (;;) {
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(p.gather.my_flags + tid) : "memory");
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(arrived) : "memory");
                 if (seen >= target) break;
                 if (++spins > p.gather.poll_limit) {
                     atomicOr(p.gather.err, 1u);
@@ -272,7 +296,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             gc = cc.hy % p.gchunks;
             head0 = kvh * p.group + gc * kHeadsPerCta;
             nh = min(static_cast<uint32_t>(kHeadsPerCta), p.group - gc * kHeadsPerCta);
-            const float* qrow = p.q + (static_cast<size_t>(cc.seq) * p.q_heads + head0 + g) * D;
+            const float* qrow = p.q + (static_cast<size_t>(seq_base + cc.seq) * p.q_heads + head0 + g) * D;
             const bool live = static_cast<uint32_t>(g) < nh;
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
@@ -320,7 +344,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 const bool is_v = lane >= 16;
                 if (ch < kChunksPerRow) {
                     const float* src = (is_v ? p.v_new : p.k_new) +
-                                       (static_cast<size_t>(cc.seq) * p.layer.kv_heads + kvh) * D + ch * 8;
+                                       (static_cast<size_t>(seq_base + cc.seq) * p.layer.kv_heads + kvh) * D + ch * 8;
                     const uint4 packed = pack8(*reinterpret_cast<const float4*>(src),
                                                *reinterpret_cast<const float4*>(src + 4));
                     const uint32_t soff = row * kRowBytes + ((ch ^ (row & 7)) << 4);
@@ -488,15 +512,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             // which CTAs share this cell, and which of them this one is
             if (i + 1 == ntiles) ITK_TRACE(p, 13);
             uint32_t n_parts = al_parts, part = al_part;
-            if (!aligned) decode_cell_parts(blockIdx.x, cum[cc.seq] + cc.hy * cc.T, cc.T, per, &n_parts, &part);
-            finish_unit<kDecodeThreads, kDecodeMaxParts>(p, cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm, fl, flag,
-                                                         wscratch);
+            if (!aligned) decode_cell_parts(cta, cum[cc.seq] + cc.hy * cc.T, cc.T, per, &n_parts, &part);
+            finish_unit<kDecodeThreads, kDecodeMaxParts>(p, seq_base + cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm,
+                                                         fl, flag, wscratch, glane);
             fresh = true;
         }
         advance(cc);
     }
     cp_async_wait<0>();
     ITK_TRACE(p, 7);
+    // A launch that never waited for its predecessor does so now, so that grids complete in stream order and
+    // whatever follows the loop in the stream sees all of it done.
+    if (p.pdl == 3) pdl_wait();
 }
 
 constexpr int kStages128 = 3;  // 96 KiB of pipeline per CTA at D = 128, two CTAs per SM

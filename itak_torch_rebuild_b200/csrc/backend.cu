@@ -119,9 +119,14 @@ struct itk_backend {
     uint64_t res_max_steps = 0;
     uint32_t res_ctas = 0, res_parts = 0;
     uint32_t res_launches_in_step = 0;
+    // two-lane schedule of the loop's gathering launches (see GatherTarget): 1 = off
+    uint32_t res_lanes = 1, res_lane_split = 0, res_lane_ctas = 0;
+    int lanes_mode = 1;        // option decode_lanes: 0 = never, 1 = when a launch is short enough to gain, 2 = whenever possible
+    bool lane_stagger = true;  // option decode_lane_stagger: lane 1 of a step's first launch starts behind lane 0
     // fused gather: one allocation per rank = [256-byte header: flags[8], err @64, base_pos @128][data]
     unsigned char* gth_local = nullptr;
     unsigned char* gth_peer[itk::kMaxPeers] = {};
+    bool gth_attached[itk::kMaxPeers] = {};  // the caller's mapping (itk_gather_attach): not closed by the backend
     uint32_t gth_world = 0, gth_rank = 0;
     uint64_t gth_bytes = 0;
     uint32_t gth_poll_limit = 200000;  // option gather_poll_limit: polls of a peer's arrival flag before giving up
@@ -138,6 +143,12 @@ struct itk_backend {
     };
     std::vector<LayerPrep> prep;
     float *d_qp = nullptr, *d_kp = nullptr;  // prepared rows, stage_rows each (allocated with the first config)
+    // whole-forward host call: per-layer staging on the device, two copy streams and per-layer events (lazy)
+    float *fw_q = nullptr, *fw_k = nullptr, *fw_v = nullptr, *fw_out = nullptr;
+    size_t fw_rows = 0;  // rows (sequences x rows per sequence) each layer's staging holds
+    cudaStream_t fw_in = nullptr, fw_outs = nullptr;
+    std::vector<cudaEvent_t> fw_ev_in, fw_ev_k;
+    cudaEvent_t fw_ev_prev = nullptr;
     // profiling: event pairs (start, stop) tagged 0 = attention, 1 = append, 2 = snapshot gather / restore scatter
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_tags;
@@ -707,9 +718,18 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->d_status);
     if (b->h_status) cudaFreeHost(b->h_status);
     for (uint32_t j = 0; j < itk::kMaxPeers; ++j)
-        if (b->gth_peer[j] && j != b->gth_rank) cudaIpcCloseMemHandle(b->gth_peer[j]);
+        if (b->gth_peer[j] && j != b->gth_rank && !b->gth_attached[j]) cudaIpcCloseMemHandle(b->gth_peer[j]);
     cudaFree(b->gth_local);
     for (cudaEvent_t e : b->prof_events) cudaEventDestroy(e);
+    cudaFree(b->fw_q);
+    cudaFree(b->fw_k);
+    cudaFree(b->fw_v);
+    cudaFree(b->fw_out);
+    for (cudaEvent_t e : b->fw_ev_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : b->fw_ev_k) cudaEventDestroy(e);
+    if (b->fw_ev_prev) cudaEventDestroy(b->fw_ev_prev);
+    if (b->fw_in) cudaStreamDestroy(b->fw_in);
+    if (b->fw_outs) cudaStreamDestroy(b->fw_outs);
     if (b->own_stream) cudaStreamDestroy(b->own_stream);
     delete b;
 }
@@ -735,6 +755,12 @@ int itk_set_option(itk_backend* b, const char* name, int64_t value) {
         (key == "decode_splits" ? b->forced_splits : b->forced_ctas) = static_cast<int>(value);
         return ITK_OK;
     }
+    if (key == "decode_lanes") {
+        if (value < 0 || value > 2) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: decode_lanes is 0, 1 or 2");
+        b->lanes_mode = static_cast<int>(value);
+        return ITK_OK;
+    }
+    if (key == "decode_lane_stagger") return flag(&b->lane_stagger);
     if (key == "pdl") return flag(&b->use_pdl);
     if (key == "decode_fused_sum") return flag(&b->fused_sum);
     if (key == "separate_append") return flag(&b->separate_append);
@@ -898,6 +924,51 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
             12ull * w1 <= 13ull * w0)
             ctas -= cells;
     }
+    // Two lanes for the gathering launches: cut the batch where the tiles of layer 0 balance best, give each half one
+    // CTA per SM, and take the schedule only if every cell of either lane stays within the scratch's partial slots on
+    // every layer at the first and the last step - and, unless asked for regardless, only when a launch is short
+    // enough (at most kLaneTilesPerCta tiles per CTA) for the hand-over between layers to matter.
+    uint32_t lanes = 1, lane_split = 0;
+    const uint32_t lane_ctas = 2u * static_cast<uint32_t>(b->sm_count);
+    if (b->lanes_mode != 0 && n_seqs >= 2 && b->forced_ctas <= 0) {
+        constexpr uint64_t kLaneTilesPerCta = 96;
+        auto lane_tiles = [&](uint32_t l, uint32_t s0, uint32_t s1, uint64_t extra, uint64_t* tmax, uint64_t* total) {
+            *tmax = 0;
+            *total = 0;
+            for (uint32_t i = s0; i < s1; ++i) {
+                uint64_t n = static_cast<uint64_t>(states[i].pos) + 1 + extra;
+                if (b->window[l] && n > b->window[l]) n = b->window[l];
+                const uint64_t t = (n + 63) / 64;
+                if (t > *tmax) *tmax = t;
+                *total += t * HY;
+            }
+        };
+        uint64_t tm, whole, best_gap = ~0ull;
+        lane_tiles(0, 0, n_seqs, 0, &tm, &whole);
+        for (uint32_t s = 1; s < n_seqs; ++s) {
+            uint64_t left;
+            lane_tiles(0, 0, s, 0, &tm, &left);
+            const uint64_t gap = 2 * left > whole ? 2 * left - whole : whole - 2 * left;
+            if (gap < best_gap) {
+                best_gap = gap;
+                lane_split = s;
+            }
+        }
+        bool ok = b->lanes_mode == 2 || whole <= kLaneTilesPerCta * lane_ctas;
+        const uint64_t g = lane_ctas / 2;
+        for (uint32_t l = 0; l < b->cfg.n_layers && ok; ++l)
+            for (int half = 0; half < 2 && ok; ++half) {
+                const uint32_t s0 = half ? lane_split : 0, s1 = half ? n_seqs : lane_split;
+                uint64_t ts, tots, te, tote;
+                lane_tiles(l, s0, s1, 0, &ts, &tots);
+                lane_tiles(l, s0, s1, max_steps - 1, &te, &tote);
+                const uint32_t ps = static_cast<uint32_t>((tots + g - 1) / g), pe = static_cast<uint32_t>((tote + g - 1) / g);
+                ok = itk::decode_parts_for(static_cast<uint32_t>(ts), ps) <= cap &&
+                     itk::decode_parts_for(static_cast<uint32_t>(te), pe) <= cap &&
+                     itk::decode_parts_for(static_cast<uint32_t>(te), ps) <= cap;
+            }
+        if (ok) lanes = 2;
+    }
     ITK_CUDA(b, cudaMemcpyAsync(b->d_states, states.data(), n_seqs * sizeof(itk::SeqState), cudaMemcpyHostToDevice,
                                 b->stream), "sequence-state upload");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
@@ -913,6 +984,9 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
     b->res_max_steps = max_steps;
     b->res_ctas = static_cast<uint32_t>(ctas);
     b->res_parts = static_cast<uint32_t>(cap);
+    b->res_lanes = lanes;
+    b->res_lane_split = lane_split;
+    b->res_lane_ctas = lane_ctas;
     b->res_prev_layer = -1;
     b->res_launches_in_step = 0;
     if (b->gth_local) {
@@ -941,6 +1015,7 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
     if (int rc = check_layer(b, layer)) return rc;
     AttnLaunch p{};
+    bool two_lanes = false;
     fill_layer_view(b, layer, &p.layer);
     p.q = d_q;
     p.out = d_out;
@@ -982,14 +1057,23 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
         p.gather.base_pos = reinterpret_cast<const uint32_t*>(b->gth_local + 128);
         p.gather.launches_per_step = b->cfg.n_layers;
         p.gather.launches_before = b->res_launches_in_step;
-        p.gather.cells = p.n_seqs * b->cfg.kv_heads * b->gchunks;
+        const uint32_t HY = b->cfg.kv_heads * b->gchunks;
+        two_lanes = b->res_lanes == 2;
+        p.gather.lanes = two_lanes ? 2u : 1u;
+        p.gather.lane_split = two_lanes ? b->res_lane_split : 0u;
+        p.gather.lane_cells[0] = (two_lanes ? b->res_lane_split : p.n_seqs) * HY;
+        p.gather.lane_cells[1] = two_lanes ? (p.n_seqs - b->res_lane_split) * HY : 0u;
+        p.gather.stagger = (two_lanes && b->lane_stagger && b->use_pdl && b->res_launches_in_step == 0) ? 1u : 0u;
         p.gather.wait_prev = 1u;
         p.gather.poll_limit = b->gth_poll_limit;
     }
     // Early K/V loads are safe behind another layer's decode kernel; behind anything else (the position advance,
-    // the same layer) the kernel waits first.
-    p.pdl = !b->use_pdl ? 0u : ((b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer) ? 2u : 1u);
-    ITK_CUDA(b, itk::launch_decode_f16_resident(p, b->res_ctas, b->res_parts, b->stream, &b->stats.kernel_launches),
+    // the same layer) the kernel waits first.  A two-lane launch behind another layer's does not wait for it at all
+    // before working: its lanes' arrival counters order what the two launches share.
+    const bool behind_other_layer = b->res_prev_layer >= 0 && static_cast<uint32_t>(b->res_prev_layer) != layer;
+    p.pdl = !b->use_pdl ? 0u : (behind_other_layer ? (two_lanes ? 3u : 2u) : 1u);
+    ITK_CUDA(b, itk::launch_decode_f16_resident(p, two_lanes ? b->res_lane_ctas : b->res_ctas, b->res_parts, b->stream,
+                                                &b->stats.kernel_launches),
              "resident decode launch");
     b->res_prev_layer = static_cast<int>(layer);
     b->res_launches_in_step += 1;
@@ -1046,6 +1130,17 @@ int itk_gather_open(itk_backend* b, uint32_t peer_rank, const uint8_t* handle64)
     void* ptr = nullptr;
     ITK_CUDA(b, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
     b->gth_peer[peer_rank] = static_cast<unsigned char*>(ptr);
+    return ITK_OK;
+}
+
+int itk_gather_attach(itk_backend* b, uint32_t peer_rank, void* peer_local_data) {
+    if (!b || !peer_local_data) return ITK_ERR_INVALID_ARGUMENT;
+    if (!b->gth_local || peer_rank >= b->gth_world)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: create the local buffer first; rank must be < world");
+    if (peer_rank == b->gth_rank) return ITK_OK;
+    if (b->gth_peer[peer_rank]) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: rank " + zu(peer_rank) + " is already open");
+    b->gth_peer[peer_rank] = static_cast<unsigned char*>(peer_local_data) - 256;  // the header sits before the data
+    b->gth_attached[peer_rank] = true;
     return ITK_OK;
 }
 
@@ -1167,6 +1262,74 @@ int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const u
     ITK_CUDA(b, cudaMemcpyAsync(out, b->d_out, qb, cudaMemcpyDeviceToHost, b->stream), "output download");
     queue_status_read(b);
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "attention");
+    return check_status(b);
+}
+
+int itk_attention_layers_host(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, const uint64_t* positions,
+                              uint32_t rows, const float* q, const float* k, const float* v, float* out) {
+    if (!b || !slots || !positions || !q || !k || !v || !out) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    const uint32_t L = b->cfg.n_layers;
+    // Every layer is validated before anything is queued: a refusal leaves all layers where they were.
+    std::vector<SeqDesc> seqs;
+    for (uint32_t l = 0; l < L; ++l)
+        if (int rc = validate_step(b, l, n_seqs, slots, positions, rows, &seqs)) return rc;
+    const size_t total_rows = static_cast<size_t>(n_seqs) * rows;
+    if (total_rows > b->stage_rows)
+        return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(total_rows) + " rows exceed the staging capacity of " +
+                                             zu(b->stage_rows));
+    if (b->fw_rows < total_rows) {  // first use (or a larger batch): per-layer staging, copy streams, events
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "forward staging");
+        cudaFree(b->fw_q);
+        cudaFree(b->fw_k);
+        cudaFree(b->fw_v);
+        cudaFree(b->fw_out);
+        b->fw_q = b->fw_k = b->fw_v = b->fw_out = nullptr;
+        b->fw_rows = 0;
+        const size_t rows_cap = b->stage_rows;
+        ITK_CUDA(b, cudaMalloc(&b->fw_q, L * rows_cap * b->q_width() * sizeof(float)), "forward staging allocation");
+        ITK_CUDA(b, cudaMalloc(&b->fw_out, L * rows_cap * b->q_width() * sizeof(float)), "forward staging allocation");
+        ITK_CUDA(b, cudaMalloc(&b->fw_k, L * rows_cap * b->row_len() * sizeof(float)), "forward staging allocation");
+        ITK_CUDA(b, cudaMalloc(&b->fw_v, L * rows_cap * b->row_len() * sizeof(float)), "forward staging allocation");
+        b->fw_rows = rows_cap;
+        if (!b->fw_in) ITK_CUDA(b, cudaStreamCreateWithFlags(&b->fw_in, cudaStreamNonBlocking), "copy stream");
+        if (!b->fw_outs) ITK_CUDA(b, cudaStreamCreateWithFlags(&b->fw_outs, cudaStreamNonBlocking), "copy stream");
+        if (!b->fw_ev_prev) ITK_CUDA(b, cudaEventCreateWithFlags(&b->fw_ev_prev, cudaEventDisableTiming), "event");
+        while (b->fw_ev_in.size() < L) {
+            cudaEvent_t a, c;
+            ITK_CUDA(b, cudaEventCreateWithFlags(&a, cudaEventDisableTiming), "event");
+            b->fw_ev_in.push_back(a);
+            ITK_CUDA(b, cudaEventCreateWithFlags(&c, cudaEventDisableTiming), "event");
+            b->fw_ev_k.push_back(c);
+        }
+    }
+    const size_t qn = total_rows * b->q_width(), kn = total_rows * b->row_len();
+    const size_t qs = b->fw_rows * b->q_width(), ks = b->fw_rows * b->row_len();  // per-layer staging strides
+    // The uploads start once everything already queued on the backend's stream (an earlier forward's kernels,
+    // which read the same staging) has run.
+    ITK_CUDA(b, cudaEventRecord(b->fw_ev_prev, b->stream), "forward");
+    ITK_CUDA(b, cudaStreamWaitEvent(b->fw_in, b->fw_ev_prev, 0), "forward");
+    // Three streams: layer l's rows go up on the first while layer l - 1 computes on the backend's stream and
+    // layer l - 2's result comes down on the third.
+    for (uint32_t l = 0; l < L; ++l) {
+        ITK_CUDA(b, cudaMemcpyAsync(b->fw_q + l * qs, q + l * qn, qn * sizeof(float), cudaMemcpyHostToDevice, b->fw_in), "q upload");
+        ITK_CUDA(b, cudaMemcpyAsync(b->fw_k + l * ks, k + l * kn, kn * sizeof(float), cudaMemcpyHostToDevice, b->fw_in), "k upload");
+        ITK_CUDA(b, cudaMemcpyAsync(b->fw_v + l * ks, v + l * kn, kn * sizeof(float), cudaMemcpyHostToDevice, b->fw_in), "v upload");
+        ITK_CUDA(b, cudaEventRecord(b->fw_ev_in[l], b->fw_in), "forward");
+    }
+    for (uint32_t l = 0; l < L; ++l) {
+        ITK_CUDA(b, cudaStreamWaitEvent(b->stream, b->fw_ev_in[l], 0), "forward");
+        if (int rc = step_device(b, l, n_seqs, slots, positions, rows, b->fw_q + l * qs, b->fw_k + l * ks, b->fw_v + l * ks,
+                                 b->fw_out + l * qs))
+            return rc;
+        ITK_CUDA(b, cudaEventRecord(b->fw_ev_k[l], b->stream), "forward");
+        ITK_CUDA(b, cudaStreamWaitEvent(b->fw_outs, b->fw_ev_k[l], 0), "forward");
+        ITK_CUDA(b, cudaMemcpyAsync(out + l * qn, b->fw_out + l * qs, qn * sizeof(float), cudaMemcpyDeviceToHost, b->fw_outs),
+                 "output download");
+    }
+    queue_status_read(b);
+    ITK_CUDA(b, cudaStreamSynchronize(b->fw_outs), "forward");
+    ITK_CUDA(b, cudaStreamSynchronize(b->stream), "forward");
     return check_status(b);
 }
 
@@ -1836,20 +1999,32 @@ extern "C" {
 
 int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* s, const char* model_fingerprint, uint8_t* out,
                          size_t capacity, size_t* size) {
+    return itk_snapshot_to_itkv_version(b, s, model_fingerprint, itk::itkv::kVersionF32, out, capacity, size);
+}
+
+int itk_snapshot_to_itkv_version(itk_backend* b, const itk_snapshot* s, const char* model_fingerprint, uint32_t version,
+                                 uint8_t* out, size_t capacity, size_t* size) {
     if (!b || !s || !model_fingerprint || !size) return ITK_ERR_INVALID_ARGUMENT;
+    if (version != itk::itkv::kVersionF32 && version != itk::itkv::kVersionTyped)
+        return b->fail(ITK_ERR_UNSUPPORTED_VERSION, "snapshot: unsupported format version " + zu(version));
+    // version 1 always carries f32 rows; version 2 carries the snapshot's own element type
+    const bool halves_out = version == itk::itkv::kVersionTyped && s->f16;
+    const size_t out_elem = halves_out ? 2 : 4;
     const size_t fp_len = std::strlen(model_fingerprint);
     const size_t n_layers = s->rows.size();
     const size_t row = static_cast<size_t>(s->kv_heads) * s->head_dim;
     size_t payload = 0;
-    for (size_t l = 0; l < n_layers; ++l) payload += static_cast<size_t>(s->rows[l]) * row * 2 * sizeof(float);
-    const size_t total = 4 + 4 + 4 + fp_len + 8 + 4 + 4 + 4 + 28 * n_layers + payload + 8;
+    for (size_t l = 0; l < n_layers; ++l) payload += static_cast<size_t>(s->rows[l]) * row * 2 * out_elem;
+    const size_t total = 4 + 4 + (version == itk::itkv::kVersionTyped ? 4 : 0) + 4 + fp_len + 8 + 4 + 4 + 4 + 28 * n_layers +
+                         payload + 8;
     *size = total;
     if (!out) return ITK_OK;
     if (capacity < total)
         return b->fail(ITK_ERR_CAPACITY, "snapshot encode: buffer holds " + zu(capacity) + " bytes, " + zu(total) + " needed");
     std::vector<uint8_t> head;
     head.insert(head.end(), {'I', 'T', 'K', 'V'});
-    put_u32(head, 1);
+    put_u32(head, version);
+    if (version == itk::itkv::kVersionTyped) put_u32(head, s->f16 ? itk::itkv::kElemF16 : itk::itkv::kElemF32);
     put_u32(head, static_cast<uint32_t>(fp_len));
     head.insert(head.end(), model_fingerprint, model_fingerprint + fp_len);
     put_u64(head, s->token_count);
@@ -1872,8 +2047,15 @@ int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* s, const char* mode
         const size_t elems = static_cast<size_t>(s->rows[l]) * row;
         if (elems == 0) continue;
         uint8_t* kbytes = out + at;  // may be unaligned for f32: filled through memcpy below
-        uint8_t* vbytes = out + at + elems * sizeof(float);
-        if (!s->f16) {
+        uint8_t* vbytes = out + at + elems * out_elem;
+        if (halves_out) {
+            // the half bit patterns as they sit in the cache (this host is little-endian, like the format)
+            halves.resize(2 * elems);
+            if (int rc = itk_snapshot_layer_to_host(b, s, static_cast<uint32_t>(l), halves.data(), halves.data() + elems, nullptr, nullptr))
+                return rc;
+            std::memcpy(kbytes, halves.data(), elems * 2);
+            std::memcpy(vbytes, halves.data() + elems, elems * 2);
+        } else if (!s->f16) {
             // the payload offset is arbitrary, so download to aligned scratch and copy the bytes
             std::vector<float> tmp(2 * elems);
             if (int rc = itk_snapshot_layer_to_host(b, s, static_cast<uint32_t>(l), tmp.data(), tmp.data() + elems, nullptr, nullptr))
@@ -1890,7 +2072,7 @@ int itk_snapshot_to_itkv(itk_backend* b, const itk_snapshot* s, const char* mode
                 std::memcpy(vbytes + 4 * i, &vf, 4);
             }
         }
-        at += 2 * elems * sizeof(float);
+        at += 2 * elems * out_elem;
     }
     const uint64_t sum = fnv1a64(out, at);
     for (int i = 0; i < 8; ++i) out[at + i] = static_cast<uint8_t>(sum >> (8 * i));
@@ -1923,16 +2105,65 @@ int itk_snapshot_from_itkv(itk_backend* b, const uint8_t* bytes, size_t n, const
             return b->fail(ITK_ERR_FINGERPRINT_MISMATCH,
                            std::string("fingerprint mismatch: expected ") + expected_fingerprint + ", snapshot has " + have);
     }
-    // the payload sits at arbitrary byte offsets: copy the rows into aligned storage before the upload
+    if (parsed.elem_bytes == 2 && b->f16) {
+        // Half rows into a half cache: the bit patterns are installed as they are (no conversion, no rounding).
+        itk_snapshot* s = new (std::nothrow) itk_snapshot();
+        if (!s) return b->fail(ITK_ERR_CUDA, "out of host memory");
+        cudaSetDevice(b->cfg.device);
+        s->device = b->cfg.device;
+        s->f16 = true;
+        s->kv_heads = hkv;
+        s->head_dim = hd;
+        s->window = b->window;
+        s->token_count = token_count;
+        uint64_t at = 0;
+        for (uint32_t l = 0; l < layer_count; ++l) {
+            s->first.push_back(firsts[l]);
+            s->rows.push_back(rows[l]);
+            s->k_off.push_back(at);
+            at += rows[l] * row;
+            s->v_off.push_back(at);
+            at += rows[l] * row;
+        }
+        s->total_elems = at;
+        if (at) {
+            cudaError_t e = cudaMalloc(&s->data, at * 2);
+            for (uint32_t l = 0; l < layer_count && e == cudaSuccess; ++l) {
+                const size_t nbytes = static_cast<size_t>(rows[l] * row) * 2;
+                if (nbytes == 0) continue;
+                unsigned char* base = static_cast<unsigned char*>(s->data);
+                e = cudaMemcpyAsync(base + s->k_off[l] * 2, kptr[l], nbytes, cudaMemcpyHostToDevice, b->stream);
+                if (e == cudaSuccess)
+                    e = cudaMemcpyAsync(base + s->v_off[l] * 2, vptr[l], nbytes, cudaMemcpyHostToDevice, b->stream);
+            }
+            if (e == cudaSuccess) e = cudaStreamSynchronize(b->stream);  // the source bytes belong to the caller
+            if (e != cudaSuccess) {
+                itk_snapshot_free(s);
+                return b->cuda_fail(e, "snapshot import");
+            }
+        }
+        *out = s;
+        return ITK_OK;
+    }
+    // the payload sits at arbitrary byte offsets: copy the rows into aligned storage before the upload (half rows
+    // bound for an f32 cache are widened exactly on the way)
     std::vector<std::vector<float>> ks(layer_count), vs(layer_count);
     std::vector<const float*> kp(layer_count), vp(layer_count);
     for (uint32_t l = 0; l < layer_count; ++l) {
         const size_t floats = static_cast<size_t>(rows[l] * row);
         ks[l].resize(floats ? floats : 1);
         vs[l].resize(floats ? floats : 1);
-        if (floats) {
+        if (floats && parsed.elem_bytes == 4) {
             std::memcpy(ks[l].data(), kptr[l], floats * 4);
             std::memcpy(vs[l].data(), vptr[l], floats * 4);
+        } else if (floats) {
+            for (size_t i = 0; i < floats; ++i) {
+                uint16_t hk, hv;
+                std::memcpy(&hk, kptr[l] + 2 * i, 2);
+                std::memcpy(&hv, vptr[l] + 2 * i, 2);
+                ks[l][i] = half_bits_to_float(hk);
+                vs[l][i] = half_bits_to_float(hv);
+            }
         }
         kp[l] = ks[l].data();
         vp[l] = vs[l].data();

@@ -89,13 +89,22 @@ inline bool valid_utf8(const uint8_t* s, size_t n) {
     return true;
 }
 
+// Format versions.  Version 1 is the reference's: f32 rows.  Version 2 (this library's extension for f16 caches,
+// which the reference refuses to snapshot, crates/wgpu-compute/src/session.rs:383-398) is the same layout with one
+// more header field - a u32 element type directly after the version, 0 = f32, 1 = IEEE half - and rows stored in
+// that type, little-endian; everything else, the checksum included, is unchanged.
+constexpr uint32_t kVersionF32 = 1, kVersionTyped = 2;
+constexpr uint32_t kElemF32 = 0, kElemF16 = 1;
+
 // A decoded, validated snapshot: geometry, per-layer headers and where each layer's rows sit in the bytes.
 struct Parsed {
+    uint32_t version = kVersionF32;
+    uint32_t elem_bytes = 4;  // 4 = f32 rows, 2 = half rows (version 2 only)
     std::string fingerprint;
     uint64_t token_count = 0;
     uint32_t kv_heads = 0, head_dim = 0, layer_count = 0;
     std::vector<uint64_t> windows, firsts, rows;  // per layer: 0 = global or the window; first position; row count
-    std::vector<const uint8_t*> kptr, vptr;       // per layer: f32 LE rows inside `bytes` (unaligned)
+    std::vector<const uint8_t*> kptr, vptr;       // per layer: little-endian rows inside `bytes` (unaligned)
 };
 
 // KvSnapshot::from_bytes followed by KvSnapshot::validate (snapshot.rs:187-236, 381-540).  Returns ITK_OK or the
@@ -116,7 +125,15 @@ inline int parse(const uint8_t* bytes, size_t n, Parsed* out, std::string* why) 
     if (std::memcmp(p, "ITKV", 4) != 0) return fail(ITK_ERR_BAD_MAGIC, "snapshot: bad magic");
     uint32_t version;
     if (!r.u32(&version)) return truncated(r, 4);
-    if (version != 1) return fail(ITK_ERR_UNSUPPORTED_VERSION, "snapshot: unsupported format version " + zu(version));
+    if (version != kVersionF32 && version != kVersionTyped)
+        return fail(ITK_ERR_UNSUPPORTED_VERSION, "snapshot: unsupported format version " + zu(version));
+    uint64_t elem_bytes = 4;
+    if (version == kVersionTyped) {
+        uint32_t elem;
+        if (!r.u32(&elem)) return truncated(r, 4);
+        if (elem == kElemF16) elem_bytes = 2;
+        else if (elem != kElemF32) return inconsistent("element type tag " + zu(elem) + " is not a known type");
+    }
     uint32_t fp_len;
     if (!r.u32(&fp_len)) return truncated(r, 4);
     const uint8_t* fp;
@@ -157,7 +174,7 @@ inline int parse(const uint8_t* bytes, size_t n, Parsed* out, std::string* why) 
     for (uint32_t l = 0; l < layer_count; ++l) {
         uint64_t floats, nbytes;
         if (__builtin_mul_overflow(rows[l], row, &floats)) return inconsistent("layer row count overflows the row width");
-        if (__builtin_mul_overflow(floats, static_cast<uint64_t>(4), &nbytes))
+        if (__builtin_mul_overflow(floats, elem_bytes, &nbytes))
             return inconsistent("float count overflows the byte count");
         if (!r.take(nbytes, &kptr[l])) return truncated(r, nbytes);
         if (!r.take(nbytes, &vptr[l])) return truncated(r, nbytes);
@@ -179,6 +196,8 @@ inline int parse(const uint8_t* bytes, size_t n, Parsed* out, std::string* why) 
         if (rows[l] != want_rows)
             return inconsistent("layer " + zu(l) + ": holds " + zu(rows[l]) + " rows but " + zu(want_rows) + " rows were expected");
     }
+    out->version = version;
+    out->elem_bytes = static_cast<uint32_t>(elem_bytes);
     out->fingerprint.assign(reinterpret_cast<const char*>(fp), fp_len);
     out->token_count = token_count;
     out->kv_heads = hkv;

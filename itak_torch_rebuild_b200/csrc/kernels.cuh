@@ -54,19 +54,29 @@ constexpr int kMaxPeers = 8;  // GPUs of one box
 
 // The per-layer gather of head outputs done by the decode kernel itself: the CTA that writes a cell's final
 // output stores it into the same place of every rank's gather buffer (plain stores to peer-mapped memory over
-// NVLink) and then bumps entry [my_rank] of every rank's flag array, so a consumer on rank j knows that rank r has
-// delivered c cells once flags_j[r] >= c.
+// NVLink) and then bumps entry [lane][my_rank] of every rank's flag array, so a consumer on rank j knows that rank r
+// has delivered c cells of a lane once flags_j[lane][r] >= c.
+//
+// Lanes.  A layer's inputs for one sequence depend on the previous layer's gathered outputs of THAT sequence only, so
+// the batch can run as two halves ("lanes": sequences [0, lane_split) and [lane_split, n_seqs)) that are out of phase
+// with each other: while one lane's outputs cross NVLink and the next layer waits for them, the other lane streams
+// its cache.  With lanes == 2 the first half of the grid's CTAs serves lane 0 and the second half lane 1 (one CTA of
+// each per SM), every lane has its own arrival counters, and a CTA waits for its own lane's previous launch only.
 struct GatherTarget {
     uint32_t n_peers;                    // 0 = outputs go to AttnLaunch::out only
     uint32_t my_rank;
     float* peer_out[kMaxPeers];          // this rank's [n_seqs][q_heads][D] slot inside every rank's buffer
-    unsigned int* peer_flags[kMaxPeers]; // every rank's flag array (kMaxPeers entries)
+    unsigned int* peer_flags[kMaxPeers]; // every rank's flag array ([2 lanes][kMaxPeers] entries)
     const unsigned int* my_flags;        // the local flag array, written by the peers
     unsigned int* err;                   // local word: bit 0 = a bounded wait ran out
     const uint32_t* base_pos;            // device word: position of sequence 0 when the loop began
     uint32_t launches_per_step;          // decode launches of one step of the loop
     uint32_t launches_before;            // decode launches of this step that precede this one
-    uint32_t cells;                      // cells every rank delivers per launch
+    uint32_t lanes;                      // 1, or 2 = the two-lane schedule described above
+    uint32_t lane_split;                 // first sequence of lane 1
+    uint32_t lane_cells[2];              // cells every rank delivers per launch, per lane (lane 0 = all when lanes == 1)
+    uint32_t stagger;                    // 1 = (first launch of a step, two lanes) lane 1 starts once lane 0's cells of
+                                         // this launch are out on this rank, which puts the lanes out of phase
     uint32_t wait_prev;                  // 1 = before using its inputs, check that every peer's previous launch arrived
     uint32_t poll_limit;                 // polls of one arrival flag before the wait gives up and records that
 };
@@ -95,7 +105,10 @@ struct AttnLaunch {
                              // instead of a separate append launch
     uint32_t pdl;            // decode and tcgen05 multi-row kernels launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
-                             // K/V tile loads are in flight (nothing the predecessor writes is read before the wait)
+                             // K/V tile loads are in flight (nothing the predecessor writes is read before the wait),
+                             // 3 = (decode kernel, two lanes) never wait for the predecessor before working - the
+                             // lane's arrival counters order everything that is shared with it - and wait for it just
+                             // before the CTA exits, so that grids still complete in stream order
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size

@@ -1,7 +1,7 @@
-// The persistent prefix store: one file per entry under a root directory, entries keyed by token prefix, the whole
-// store bounded by a byte cap with least-recently-used eviction.  Host code only (no kernel lives here); the
-// payload of an entry is an ITKV snapshot (itk_snapshot_to_itkv / itk_snapshot_from_itkv move it to and from the
-// device).
+// Prefix snapshots kept on disk between runs.  Each stored prefix is a file of its own inside one directory; a
+// lookup finds the longest stored run of token ids that starts the query; a byte budget caps the directory and the
+// entries that were used longest ago are deleted first when it is exceeded.  Everything here runs on the host: an
+// entry's payload is an ITKV snapshot, which itk_snapshot_to_itkv / itk_snapshot_from_itkv carry to and from the GPU.
 //
 // Stands in for crates/itak-kv/src/store.rs (entry layout :5-21, trust model :23-33, atomic writes :35-39,
 // last-used stamping and eviction :41-46, index by scan at open :48-52) and writes the same bytes under the same
@@ -517,6 +517,25 @@ int itk_prefix_store_entry(const itk_prefix_store* s, uint64_t i, char* file_nam
     if (bytes) *bytes = e.bytes;
     if (created_unix) *created_unix = e.created;
     if (last_used_unix) *last_used_unix = e.last_used;
+    return ITK_OK;
+}
+
+// KvSnapshot::from_bytes + validate (crates/itak-kv/src/snapshot.rs:187-236, 425-540) without a device: the strict
+// decode alone, for callers that want to vet bytes before handing them to a backend.
+int itk_itkv_check(const uint8_t* bytes, size_t n, uint32_t* version, uint64_t* token_count, uint32_t* elem_bytes,
+                   char* why, size_t why_len) {
+    if (why && why_len) why[0] = '\0';
+    if (!bytes) return ITK_ERR_INVALID_ARGUMENT;
+    itk::itkv::Parsed parsed;
+    std::string text;
+    const int rc = itk::itkv::parse(bytes, n, &parsed, &text);
+    if (rc != ITK_OK) {
+        if (why && why_len) snprintf(why, why_len, "%s", text.c_str());
+        return rc;
+    }
+    if (version) *version = parsed.version;
+    if (token_count) *token_count = parsed.token_count;
+    if (elem_bytes) *elem_bytes = parsed.elem_bytes;
     return ITK_OK;
 }
 

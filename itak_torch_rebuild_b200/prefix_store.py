@@ -105,3 +105,15 @@ class PrefixStore:
                                                          C.byref(c), C.byref(u)))
             out.append(EntryMeta(name.value.decode(), h.value, n.value, b.value, c.value, u.value))
         return out
+
+
+def check_itkv(data: bytes):
+    """Strictly decode ITKV bytes on the host (no device): returns (version, token_count, bytes per stored element)
+    or raises the named refusal."""
+    lib = _lib.load()
+    version, tokens, elem = C.c_uint32(), C.c_uint64(), C.c_uint32()
+    why = C.create_string_buffer(512)
+    rc = lib.itk_itkv_check(data, len(data), C.byref(version), C.byref(tokens), C.byref(elem), why, len(why))
+    if rc != _lib.OK:
+        raise CudaComputeError(rc, why.value.decode("utf-8", "replace"))
+    return version.value, tokens.value, elem.value

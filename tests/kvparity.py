@@ -2,6 +2,8 @@
 compare them on the same seeded inputs."""
 from __future__ import annotations
 
+import struct
+
 import numpy as np
 
 from itak_torch_rebuild_b200 import CudaCompute, KvDtype
@@ -73,3 +75,18 @@ def assert_attention_close(got, want, hq, d, dtype, what=""):
     err = attention_error(got, want, hq, d)
     assert err <= tol, f"{what}: error {err:.3e} of the output norm exceeds {tol:.0e}"
     return err
+
+
+def typed_itkv_bytes(snapshot, fingerprint, hkv, d, window, half):
+    """Version 2 of the wire format written out by hand from its documented layout: magic, u32 version 2, u32 element
+    type (0 = f32, 1 = half), then the version-1 fields, rows in the element type, FNV-1a-64 over all of it."""
+    fp = fingerprint.encode()
+    out = bytearray(b"ITKV" + struct.pack("<III", 2, 1 if half else 0, len(fp)) + fp)
+    out += struct.pack("<QIII", snapshot.token_count, hkv, d, len(window))
+    blocks = [snapshot.layer(i) for i in range(len(window))]
+    for w, (first, k, _) in zip(window, blocks):
+        out += struct.pack("<B3xQQQ", 1 if w else 0, w, first, k.size // (hkv * d))
+    for _, k, v in blocks:
+        for rows in (k, v):
+            out += (orc.f32_to_f16_bits(rows).astype("<u2") if half else rows.astype("<f4")).tobytes()
+    return bytes(out + struct.pack("<Q", orc.checksum(bytes(out))))

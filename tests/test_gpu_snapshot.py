@@ -6,7 +6,8 @@ import pytest
 from itak_torch_rebuild_b200 import CudaCompute, CudaComputeError, KvDtype, PositionCache, _lib
 from oracle import oracle as orc
 
-from kvparity import as_f32, assert_attention_close, assert_rows_bit_equal, assert_view_equal, make_pair, stored
+from kvparity import (as_f32, assert_attention_close, assert_rows_bit_equal, assert_view_equal, make_pair, stored,
+                      typed_itkv_bytes)
 
 pytestmark = pytest.mark.gpu
 
@@ -238,9 +239,9 @@ def test_itkv_decode_refusals_are_named():
     bad = bytearray(good)
     bad[0] = ord("X")
     assert refusal(bytes(bad)).code == _lib.ERR_BAD_MAGIC
-    v2 = bytearray(good)
-    v2[4] = 2
-    assert refusal(bytes(v2)).code == _lib.ERR_UNSUPPORTED_VERSION
+    v3 = bytearray(good)
+    v3[4] = 3
+    assert refusal(bytes(v3)).code == _lib.ERR_UNSUPPORTED_VERSION
     e = refusal(good + b"\0")
     assert e.code == _lib.ERR_INCONSISTENT_SNAPSHOT and "trailing" in e.msg
     forged = b"ITKV" + struct.pack("<IIQIII", 1, 0, 0, 1, 1, 0xFFFFFFFF)
@@ -254,4 +255,78 @@ def test_itkv_decode_refusals_are_named():
     with pytest.raises(CudaComputeError) as e:
         foreign.snapshot_from_itkv(good, "model-a")
     assert e.value.code == _lib.ERR_GEOMETRY_MISMATCH
+    gpu.snapshot_from_itkv(good, "model-a")
+
+
+def test_itkv_version_2_keeps_half_rows_as_they_are():
+    """The typed format version (no counterpart in the reference, which refuses to snapshot an f16 cache,
+    crates/wgpu-compute/src/session.rs:383-398): the bytes equal the hand-written encoding of the oracle's captured
+    rows as half bit patterns, take half the payload of version 1, install bit for bit into another f16 backend, and
+    widen exactly into an f32 one; version 1 of the same snapshot still equals the oracle's f32 encoding."""
+    window, hkv, d, tokens = [4, 0, 4], 2, 8, 70
+    gpu, (ref,) = make_pair(window, 2, hkv, d, dtype=KvDtype.F16, max_context=128, chunk_cap=64)
+    fill(gpu, ref, window, hkv, d, tokens, KvDtype.F16, seed=33)
+    oracle_snap = orc.KvSnapshot.capture(ref, "model-a")
+    snap = gpu.capture_prefix_snapshot()
+    got = snap.to_itkv("model-a", version=2)
+    assert got == typed_itkv_bytes(oracle_snap, "model-a", hkv, d, window, half=True)
+    v1 = snap.to_itkv("model-a", version=1)
+    assert v1 == oracle_snap.to_bytes()
+    payload = sum(oracle_snap.layer(i)[1].size for i in range(3)) * 2
+    assert len(v1) - len(got) == payload * 2 - 4  # half the row bytes, one more header word
+
+    other = CudaCompute(3, 2, hkv, d, n_slots=1, max_context=128, chunk_cap=64, kv_dtype=KvDtype.F16, layer_window=window)
+    up = other.snapshot_from_itkv(got, expected_fingerprint="model-a")
+    assert up.token_count == tokens
+    other.install_prefix_snapshot(up)
+    for layer in range(3):
+        assert_view_equal(other, ref, layer, KvDtype.F16)
+    assert other.capture_prefix_snapshot().to_itkv("model-a", version=2) == got
+
+    wide = CudaCompute(3, 2, hkv, d, n_slots=1, max_context=128, chunk_cap=64, kv_dtype=KvDtype.F32, layer_window=window)
+    wide.install_prefix_snapshot(wide.snapshot_from_itkv(got, expected_fingerprint="model-a"))
+    for layer in range(3):
+        assert_view_equal(wide, ref, layer, KvDtype.F32)  # the oracle holds the f16-rounded values as f32
+    # an f32 cache written as version 2 declares f32 rows
+    assert wide.capture_prefix_snapshot().to_itkv("model-a", version=2) == typed_itkv_bytes(
+        oracle_snap, "model-a", hkv, d, window, half=False)
+    with pytest.raises(CudaComputeError) as e:
+        snap.to_itkv("model-a", version=3)
+    assert e.value.code == _lib.ERR_UNSUPPORTED_VERSION
+
+
+def test_itkv_version_2_decode_refusals_are_named():
+    """The strict decoder's refusals hold for the typed version too: unknown element type, truncation inside the
+    rows, trailing bytes, a flipped payload bit, and a row count whose byte size overflows."""
+    import struct
+
+    window, hkv, d = [4, 0], 2, 4
+    gpu, (ref,) = make_pair(window, 2, hkv, d, dtype=KvDtype.F16, max_context=32, chunk_cap=8)
+    fill(gpu, ref, window, hkv, d, 5, KvDtype.F16, seed=2)
+    good = gpu.capture_prefix_snapshot().to_itkv("model-a", version=2)
+
+    def refusal(data, fingerprint=None):
+        with pytest.raises(CudaComputeError) as e:
+            gpu.snapshot_from_itkv(data, fingerprint)
+        return e.value
+
+    def resum(data):
+        return bytes(data[:-8]) + struct.pack("<Q", orc.checksum(bytes(data[:-8])))
+
+    tag = bytearray(good)
+    tag[8] = 7
+    e = refusal(resum(tag))
+    assert e.code == _lib.ERR_INCONSISTENT_SNAPSHOT and "element type" in e.msg
+    assert refusal(good[:10]).code == _lib.ERR_TRUNCATED
+    assert refusal(good[: len(good) - 20]).code == _lib.ERR_TRUNCATED
+    e = refusal(good + b"\0")
+    assert e.code == _lib.ERR_INCONSISTENT_SNAPSHOT and "trailing" in e.msg
+    flipped = bytearray(good)
+    flipped[len(good) - 12] ^= 0x01
+    assert refusal(bytes(flipped)).code == _lib.ERR_CHECKSUM_MISMATCH
+    overflow = b"ITKV" + struct.pack("<III", 2, 1, 1) + b"x" + struct.pack("<QIII", 1 << 33, 65536, 65536, 1)
+    overflow += bytes(4) + struct.pack("<QQQ", 0, 0, 1 << 33)
+    overflow += struct.pack("<Q", orc.checksum(overflow))
+    assert refusal(overflow).code == _lib.ERR_INCONSISTENT_SNAPSHOT
+    assert refusal(good, "model-b").code == _lib.ERR_FINGERPRINT_MISMATCH
     gpu.snapshot_from_itkv(good, "model-a")

@@ -218,3 +218,32 @@ def test_a_taken_file_name_gets_a_counter_suffix(tmp_path):
     # putting the same tokens again reuses the suffixed name instead of taking `-c2`
     store.put(tokens, snapshot_for(tokens, "m2").to_bytes(), 9)
     assert sorted(e.file_name for e in store.entries()) == names
+
+
+def test_typed_snapshots_are_stored_and_served_and_forged_ones_refused(tmp_path):
+    """The store's payload check reads both format versions: a version-2 snapshot (half rows, this library's
+    extension for f16 caches) is put, found and returned byte for byte; one whose element type tag is unknown, or
+    whose rows stop short, is refused at the door by name."""
+    from kvparity import typed_itkv_bytes
+
+    tokens = [3, 1, 4, 1, 5]
+    snap = snapshot_for(tokens, "model-h")
+    window = [4, 0]
+    typed = typed_itkv_bytes(snap, "model-h", GEOMETRY.num_kv_heads, GEOMETRY.head_dim, window, half=True)
+    assert len(typed) < len(snap.to_bytes())
+    store = PrefixStore(str(tmp_path), 1 << 30)
+    store.put(tokens, typed, 7)
+    hit = store.lookup(tokens + [9, 2], now=8)
+    assert hit is not None and hit.token_count == 5 and hit.snapshot_bytes == typed
+
+    def resum(data):
+        return bytes(data[:-8]) + struct.pack("<Q", orc.checksum(bytes(data[:-8])))
+
+    bad_tag = bytearray(typed)
+    bad_tag[8] = 9
+    with pytest.raises(CudaComputeError) as e:
+        store.put([8, 8, 8, 8, 8], resum(bad_tag), 9)
+    assert e.value.code == _lib.ERR_INCONSISTENT_SNAPSHOT and "element type" in e.value.msg
+    with pytest.raises(CudaComputeError) as e:
+        store.put(tokens, typed[:-30], 9)
+    assert e.value.code == _lib.ERR_TRUNCATED
