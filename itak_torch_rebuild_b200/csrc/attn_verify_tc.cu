@@ -7,7 +7,8 @@
 // (crates/arch-llama/src/model.rs:212-228); row r sits at position q_pos0 + r and sees keys kp <= its
 // position (kp > position - window on a sliding layer).
 //
-// One CTA owns a (sequence, KV head, block of row-head pairs, key split).  Only the K/V stream lives in shared
+// One CTA owns a (sequence, KV head, block of row-head pairs, key split); a call of any number of rows is cut into
+// such blocks, each streaming the keys up to its own last row.  Only the K/V stream lives in shared
 // memory; everything else sits in the 512 columns of tensor memory:
 //
 //   columns   0-127  Q      row i: an f32 query as two f16 terms, [q_hi | q_lo], two halfs per column
@@ -165,8 +166,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t n_pairs = p.rows * nh;
     const uint32_t ring = p.layer.ring, window = p.layer.window;
 
-    // This CTA's slice [k0, k1) of the positions [kv_lo, kv_hi) the block can see.
-    const uint32_t n = sd.kv_hi - sd.kv_lo;
+    // This CTA's slice [k0, k1) of the positions its pair block can see: [kv_lo, kv_hi) cut off behind the block's
+    // last row (a long chunk's early row blocks do not stream the keys of its later rows).
+    const uint32_t last_pair = min(n_pairs, (pc + 1u) * PC) - 1u;
+    const uint32_t n = min(sd.kv_hi - sd.kv_lo, sd.q_pos0 + last_pair / nh + 1u - sd.kv_lo);
     uint32_t chunk = (n + p.splits - 1) / p.splits;
     chunk = (chunk + kTcTile - 1) / kTcTile * kTcTile;
     const uint32_t k0 = min(n, split * chunk);
@@ -245,7 +248,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         const float* new_src =
             new_base ? new_base + (static_cast<size_t>(seq) * p.rows * p.layer.kv_heads + kvh) * D + c * 8 : nullptr;
         const int64_t new_rel = static_cast<int64_t>(sd.q_pos0) - (static_cast<int64_t>(sd.kv_lo) + k0);
-        const bool stores_new = gc == 0 && pc == 0;
+        // the CTAs of the LAST pair block see every row of the launch: they are the ones that store them
+        const bool stores_new = gc == 0 && pc == pchunks - 1;
         for (uint32_t tile = 0; tile < ntiles; ++tile) {
             if (*abort_flag != 0) break;
             const uint32_t st = tile % nst;
@@ -753,7 +757,7 @@ uint32_t tc_pairs_for(uint32_t rows, uint32_t group) {
 
 bool verify_tc_supported(uint32_t head_dim, uint32_t rows, uint32_t group) {
     (void)group;
-    return rows >= 2 && rows <= 64 && head_dim == static_cast<uint32_t>(kTcD);
+    return rows >= 2 && head_dim == static_cast<uint32_t>(kTcD);
 }
 
 uint32_t verify_tc_pairs_per_cta(uint32_t rows, uint32_t group) { return tc_pairs_for(rows, group); }

@@ -70,13 +70,25 @@ def run_blocks(gpu, refs, layer_window, hq, hkv, n0, rows, blocks, seed):
     (7, 64, 8),    # group 8: 56 pairs
     (31, 32, 8),   # 124 pairs: one block, no replication
     (33, 32, 8),   # 132 pairs: two blocks
-    (64, 64, 8),   # 512 pairs: four blocks
+    (64, 64, 8),   # 512 pairs: eight blocks
+    (65, 32, 8),   # past the old 64-row limit: five blocks, the last one nearly empty
+    (200, 32, 8),  # a prefill chunk: thirteen blocks, each streaming the keys up to its own last row
     (5, 24, 2),    # group 12: two head chunks (8 + 4 heads)
 ])
 @pytest.mark.parametrize("n0", [0, 57, 500])
 def test_every_block_width_matches_the_oracle(rows, hq, hkv, n0):
     gpu, refs = build([0], hq, hkv, n0, rows, seed=rows + n0)
     worst, _ = run_blocks(gpu, refs, [0], hq, hkv, n0, rows, blocks=2, seed=3)
+    assert worst < TIGHT, worst
+    assert_view_equal(gpu, refs[0], 0, DTYPE)
+
+
+def test_a_whole_prefill_chunk_runs_on_the_tensor_memory_kernel():
+    """512 rows in one call (4096 row-head pairs, sixty-four blocks per KV head) behind a short prefix: every block
+    streams the keys up to its own last row only, the last block's CTAs store the chunk's rows."""
+    rows, hq, hkv, n0 = 512, 64, 8, 100
+    gpu, refs = build([0], hq, hkv, n0, rows, seed=77)
+    worst, _ = run_blocks(gpu, refs, [0], hq, hkv, n0, rows, blocks=1, seed=78)
     assert worst < TIGHT, worst
     assert_view_equal(gpu, refs[0], 0, DTYPE)
 
