@@ -444,6 +444,8 @@ def measure_decode(args, env: Dist, workload, geom, steps, warmup, *, e2e=True, 
         be.resident_end(warmup)
         position += warmup
         ctx_first = position
+        if fused and env.reduce([float(be.gather_status())])[0] != 0:
+            raise SystemExit("a bounded wait of the fused gather ran out during warm-up: the ranks are out of step")
 
         def timed_block():
             begin(steps)
@@ -578,6 +580,9 @@ def measure_decode(args, env: Dist, workload, geom, steps, warmup, *, e2e=True, 
                                   units=args.cpu_units or threads)
         cpu_rec = {"value": 1.0 / step_s, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
 
+    if world > 1 and not args.no_graph and not args.nccl_gather:
+        be.gather_close_peers()  # no rank frees its gather buffer while a peer still maps it
+        barrier()
     be.close()
     torch.cuda.set_stream(torch.cuda.default_stream(dev))
     if rank != 0:
@@ -634,13 +639,20 @@ def run_ours(args):
     if env.rank == 0 and line is not None:
         print(json.dumps(line), flush=True)
     if env.world > 1:
-        # Leave without tearing the communicator down (a teardown after graph capture has been seen to wait
-        # forever); process exit releases the peer mappings and the communicator.
         flag = env.reduce([1.0 if failed else 0.0])[0]
         env.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(1 if flag else 0)
+        code = 1 if flag else 0
+        # Orderly teardown - every graph and backend (and with them the peer mappings) is gone by now, then the
+        # communicator - under a watchdog: an earlier form of this script left a captured graph holding NCCL work
+        # alive when it destroyed the process group and waited forever there.  Should teardown ever stall again,
+        # the line above has been printed and the process leaves after ten seconds regardless.
+        watchdog = threading.Timer(10.0, lambda: os._exit(code))
+        watchdog.daemon = True
+        watchdog.start()
+        env.dist.destroy_process_group()
+        os._exit(code)
     if failed:
         raise SystemExit(1)
 

@@ -145,8 +145,8 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * "force_general" (multi-row calls take the CUDA-core kernel, default 0), "verify_tc" (multi-row calls take the
  * tcgen05 kernel, default 1), "gather_poll_limit" (polls of a peer's arrival flag before the fused gather's wait
  * gives up, default 200000), "decode_lanes" (two-lane schedule of the gathering loop: 0 never, 1 when a launch is
- * short enough to gain, 2 whenever possible; default 1), "decode_lane_stagger" (the second lane of a step's first
- * launch starts behind the first, default 1).  Unknown names and out-of-range values are refused; not allowed inside
+ * short enough to gain, 2 whenever possible; default 1), "decode_lane_stagger" (how far the second lane of a step's
+ * first launch starts behind the first, in per cent of the time the first needs to stream its keys; default 100).  Unknown names and out-of-range values are refused; not allowed inside
  * a resident loop. */
 int itk_set_option(itk_backend* b, const char* name, int64_t value);
 int itk_synchronize(itk_backend* b);
@@ -264,12 +264,12 @@ int itk_resident_end(itk_backend* b, uint64_t steps_done);
  * host channel) and open each other's; inside the replayable loop itk_resident_layer_gather then behaves like
  * itk_resident_layer, except that the CTA finishing a (sequence, head) cell stores its rows - plain stores to
  * peer-mapped memory over NVLink - at `gather_offset_bytes` of EVERY rank's buffer (the caller gives each rank
- * and layer its own offset), and counts the cell on every rank's flag array.  A short launch runs as two lanes -
- * the batch cut in two halves of about equal work, half of the grid's CTAs each, separate arrival counters - which
- * the backend keeps out of phase, so that one half's outputs cross NVLink while the other half streams its cache (a
- * layer's inputs for a sequence depend on the previous layer's gathered outputs of that sequence only).  Before a
- * kernel of the loop uses its inputs it checks, with a bounded wait, that all ranks' cells of the previous launch
- * (of its lane) have arrived
+ * and layer its own offset), and counts the cell on every rank's arrival counters, kept per sequence of the loop
+ * and source rank in the buffer's header.  A short launch runs as two lanes - the batch cut in two halves of about
+ * equal work, half of the grid's CTAs each - which the backend keeps out of phase, so that one half's outputs cross
+ * NVLink while the other half streams its cache (a layer's inputs for a sequence depend on the previous layer's
+ * gathered outputs of that sequence only).  Before a CTA of the loop uses its inputs it checks, with a bounded wait,
+ * that all ranks' cells of the previous launch have arrived for the sequences it works on
  * (itk_gather_status reports a wait that ran out: bit 0 of *error_bits; the kernel then carries on, its own outputs
  * do not depend on the peers' rows).  All ranks must call itk_gather_reset, then synchronise with
  * each other, before itk_resident_begin; a step of the loop must launch every layer exactly once. */
@@ -281,6 +281,10 @@ int itk_gather_open(itk_backend* b, uint32_t peer_rank, const uint8_t* handle64)
  * symmetric-memory allocator: `peer_local_data` is the pointer itk_gather_create returned as *local_data on that
  * peer.  The mapping stays the caller's. */
 int itk_gather_attach(itk_backend* b, uint32_t peer_rank, void* peer_local_data);
+/* Unmaps every peer's buffer (this rank's own stays until the backend is destroyed).  For an orderly shutdown every
+ * rank calls this, the ranks synchronise, and only then the backends are destroyed - so that no rank frees a buffer
+ * a peer still maps. */
+int itk_gather_close_peers(itk_backend* b);
 int itk_gather_reset(itk_backend* b);
 int itk_gather_status(itk_backend* b, uint32_t* error_bits);
 int itk_resident_layer_gather(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,

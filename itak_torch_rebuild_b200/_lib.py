@@ -124,6 +124,7 @@ SIGNATURES = {
     "itk_gather_create": (C.c_int, [_vp, _u32, _u32, _u64, C.POINTER(_vp), _vp]),
     "itk_gather_open": (C.c_int, [_vp, _u32, _vp]),
     "itk_gather_attach": (C.c_int, [_vp, _u32, _vp]),
+    "itk_gather_close_peers": (C.c_int, [_vp]),
     "itk_gather_reset": (C.c_int, [_vp]),
     "itk_gather_status": (C.c_int, [_vp, _u32p]),
     "itk_resident_layer_gather": (C.c_int, [_vp, _u32, _vp, _vp, _vp, _u64]),

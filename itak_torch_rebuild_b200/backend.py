@@ -325,6 +325,10 @@ class CudaCompute:
         returned on that peer)."""
         self._check(self._lib.itk_gather_attach(self._h, peer_rank, C.c_void_p(peer_data_ptr)))
 
+    def gather_close_peers(self):
+        """Unmap the peers' gather buffers (every rank does this, then the ranks synchronise, then ``close``)."""
+        self._check(self._lib.itk_gather_close_peers(self._h))
+
     def gather_reset(self):
         self._check(self._lib.itk_gather_reset(self._h))
 

@@ -76,8 +76,9 @@ __device__ __forceinline__ void store_out4(const AttnLaunch& p, size_t off4, flo
     if (p.out) reinterpret_cast<float4*>(p.out)[off4] = v;
     for (uint32_t j = 0; j < p.gather.n_peers; ++j) reinterpret_cast<float4*>(p.gather.peer_out[j])[off4] = v;
 }
-// After a cell's output went out: make it visible system-wide, then count it on every rank.
-__device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p, uint32_t lane = 0) {
+// After a cell's output went out: make it visible system-wide, then count it on every rank (counter of the
+// cell's sequence, `unit` = its index in the launch).
+__device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p, uint32_t unit) {
     if (p.gather.n_peers == 0) return;
     // The CTA's stores are ordered before the barrier, and one thread's system-scope fence after it is cumulative
     // over them (the grid-barrier idiom): one fence per CTA instead of one per thread.  Then a reduction per peer
@@ -87,7 +88,7 @@ __device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p, uint3
         __threadfence_system();
         ITK_TRACE(p, 15);  // (timeline build) the system-scope fence has returned
         for (uint32_t j = 0; j < p.gather.n_peers; ++j)
-            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[j] + lane * kMaxPeers + p.gather.my_rank) : "memory");
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[j] + unit * kMaxPeers + p.gather.my_rank) : "memory");
     }
 }
 
@@ -166,8 +167,7 @@ __device__ __forceinline__ void finish_weights(const float* all_ml, uint32_t n_p
 template <int THREADS, int MAXP>
 __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, uint32_t hy, uint32_t n_parts,
                                             uint32_t part, uint32_t head0, uint32_t nh, uint32_t D, const float* fo,
-                                            const float* fm, const float* fl, int* s_flag, float* wscratch,
-                                            uint32_t lane = 0) {
+                                            const float* fm, const float* fl, int* s_flag, float* wscratch) {
     const uint32_t tid = threadIdx.x;
     const uint32_t HY = p.layer.kv_heads * p.gchunks;
     const size_t out_off = (static_cast<size_t>(unit) * p.q_heads + head0) * D;  // element offset of the cell's rows
@@ -176,7 +176,7 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
             const uint32_t h = idx / D;
             store_out(p, out_off + idx, fo[idx] / fl[h]);
         }
-        signal_cell_delivered(p, lane);
+        signal_cell_delivered(p, unit);
         return;
     }
     const size_t cell = static_cast<size_t>(unit) * HY + hy;
@@ -200,10 +200,18 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
         bool in_range = true;
         for (uint32_t h = 0; h < nh; ++h) in_range = in_range && (fm[h] == -INFINITY || fabsf(fm[h]) <= kAccRange);
         if (in_range) {
+            // four channels per reduction: the accumulator's lines are hammered by every CTA of the cell at about
+            // the same time, and L2 performs same-address reductions one after another
             float* ao = p.acc_o + cell * (kHeadsPerCta * D);
-            for (uint32_t idx = tid; idx < nh * D; idx += THREADS) {
-                const float m = fm[idx / D];
-                if (m != -INFINITY) atomicAdd(ao + idx, fo[idx] * fast_exp2(m));
+            for (uint32_t idx4 = tid; idx4 < nh * D / 4; idx4 += THREADS) {
+                const float m = fm[(idx4 * 4) / D];
+                if (m != -INFINITY) {
+                    const float w = fast_exp2(m);
+                    const float4 v = *reinterpret_cast<const float4*>(fo + idx4 * 4);
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(ao + idx4 * 4), "f"(v.x * w), "f"(v.y * w),
+                                 "f"(v.z * w), "f"(v.w * w)
+                                 : "memory");
+                }
             }
             if (tid < nh && fm[tid] != -INFINITY) atomicAdd(p.acc_l + cell * kHeadsPerCta + tid, fl[tid] * fast_exp2(fm[tid]));
         } else if (tid == 0) {
@@ -239,6 +247,7 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
                 l1 = __ldcg(al + (c1 * 4) / D);
             }
             __syncthreads();  // every thread holds its share: the accumulators can be cleared for the next launch
+            ITK_TRACE(p, 10);
             const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
             if (c0 < cols) reinterpret_cast<float4*>(ao)[c0] = zero;
             if (c1 < cols) reinterpret_cast<float4*>(ao)[c1] = zero;
@@ -248,10 +257,11 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
                 const float i0 = 1.f / l0, i1 = 1.f / l1;
                 if (c0 < cols) store_out4(p, out_off / 4 + c0, make_float4(a0.x * i0, a0.y * i0, a0.z * i0, a0.w * i0));
                 if (c1 < cols) store_out4(p, out_off / 4 + c1, make_float4(a1.x * i1, a1.y * i1, a1.z * i1, a1.w * i1));
+                ITK_TRACE(p, 11);
                 // the counter is back at zero BEFORE the cell is announced: a launch that orders itself by the
                 // arrival counters alone may take its first ticket the moment it sees the announcement
                 if (tid == 0) p.tickets[cell] = 0u;
-                signal_cell_delivered(p, lane);
+                signal_cell_delivered(p, unit);
                 return;
             }
         }
@@ -319,7 +329,7 @@ __device__ __forceinline__ void finish_unit(const AttnLaunch& p, uint32_t unit, 
         }
     }
     if (tid == 0) p.tickets[cell] = 0u;  // before the announcement, as above
-    signal_cell_delivered(p, lane);
+    signal_cell_delivered(p, unit);
 }
 
 }  // namespace itk

@@ -54,7 +54,10 @@ constexpr int kDecodeWarps = 4;
 constexpr int kTileKeys = 64;  // keys per CTA tile = 16 per warp
 // Work plan in shared memory: cum[65] tiles before each sequence, abase[65] first CTA of each sequence in the
 // cell-aligned plan, then per sequence its visible keys, first storage row and slot, then the plan's mode word.
-constexpr int kPlanWords = 2 * (kMaxSeqsPerLaunch + 4) + 3 * kMaxSeqsPerLaunch + 4;
+constexpr int kPlanWords = kDecodePlanWords;
+constexpr int kPlanCum = 0, kPlanAbase = kMaxSeqsPerLaunch + 4, kPlanSn = 2 * (kMaxSeqsPerLaunch + 4),
+              kPlanSs0 = kPlanSn + kMaxSeqsPerLaunch, kPlanSlot = kPlanSs0 + kMaxSeqsPerLaunch,
+              kPlanMode = kPlanSlot + kMaxSeqsPerLaunch;  // [mode] 1 = cell-aligned plan, [mode + 1] steps done
 
 // A walker's place in the launch's tile sequence (warp-uniform).
 struct TileCursor {
@@ -82,8 +85,48 @@ __device__ __forceinline__ SeqDesc seq_of(const AttnLaunch& p, uint32_t i) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
-__global__ void advance_states_kernel(SeqState* states, uint32_t n) {
-    if (threadIdx.x < n) states[threadIdx.x].pos += 1;
+// One plan block: sequences [s0, s1) of the batch on G CTAs.  `w` is the block's kPlanWords words (shared or global
+// memory) whose per-sequence entries (kPlanSn, kPlanSs0, kPlanSlot) are already filled for the whole batch.
+__device__ __forceinline__ void fill_plan_block(uint32_t* w, uint32_t s0, uint32_t s1, uint32_t HY, uint32_t G,
+                                                uint32_t splits) {
+    const uint32_t* sn = w + kPlanSn + s0;
+    uint32_t c = 0;
+    for (uint32_t s = 0; s < s1 - s0; ++s) {
+        w[kPlanCum + s] = c;
+        c += (sn[s] + kTileKeys - 1) / kTileKeys * HY;
+    }
+    w[kPlanCum + (s1 - s0)] = c;
+    uint32_t worst;
+    const uint32_t per = G ? (c + G - 1) / G : 0u;
+    w[kPlanMode] = (G != 0 && decode_aligned_plan(sn, s1 - s0, HY, G, c, per, splits, w + kPlanAbase, &worst)) ? 1u : 0u;
+}
+
+__global__ void advance_states_kernel(SeqState* states, uint32_t n, uint32_t add, DecodePlanSpec spec, uint32_t* plan_out) {
+    __shared__ uint32_t w[kDecodePlanBlocks][kPlanWords];
+    const uint32_t tid = threadIdx.x;
+    uint32_t pos = 0;
+    if (tid < n) {
+        SeqState st = states[tid];
+        st.pos += add;
+        pos = st.pos;
+        states[tid] = st;
+        for (int b = 0; b < kDecodePlanBlocks; ++b) {
+            w[b][kPlanSn + tid] = pos + 1;  // global layers: positions 0..pos are visible
+            w[b][kPlanSs0 + tid] = 0;
+            w[b][kPlanSlot + tid] = st.slot;
+        }
+    }
+    if (plan_out == nullptr) return;
+    // (the loop's first position sits in a device word behind the blocks, not in the launch parameters: a captured
+    // step is replayed by loops that begin at other positions)
+    if (tid == 0)
+        for (int b = 0; b < kDecodePlanBlocks; ++b) w[b][kPlanMode + 1] = pos - plan_out[kDecodePlanBlocks * kPlanWords];
+    __syncthreads();
+    if (tid == 0) fill_plan_block(w[0], 0, n, spec.cells_per_seq, spec.ctas, spec.splits);
+    if (tid == 32 && spec.lane_ctas != 0) fill_plan_block(w[1], 0, spec.lane_split, spec.cells_per_seq, spec.lane_ctas / 2, spec.splits);
+    if (tid == 63 && spec.lane_ctas != 0) fill_plan_block(w[2], spec.lane_split, n, spec.cells_per_seq, spec.lane_ctas / 2, spec.splits);
+    __syncthreads();
+    for (uint32_t i = tid; i < kDecodePlanBlocks * kPlanWords; i += blockDim.x) plan_out[i] = (&w[0][0])[i];
 }
 
 template <int D, int STAGES>
@@ -129,17 +172,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     // advance) lets its own dependents start only after that wait: they may then rely on what it waited for.
     if (p.pdl == 1) pdl_wait();
     if (p.pdl != 0) pdl_launch_dependents();
-    uint32_t* abase = cum + (kMaxSeqsPerLaunch + 4);
-    uint32_t* sn_all = abase + (kMaxSeqsPerLaunch + 4);  // visible keys per sequence
-    uint32_t* ss0_all = sn_all + kMaxSeqsPerLaunch;      // storage row of its first visible key
-    uint32_t* sslot_all = ss0_all + kMaxSeqsPerLaunch;
-    uint32_t* mode = sslot_all + kMaxSeqsPerLaunch;      // [0] 1 = cell-aligned plan
-    if (static_cast<uint32_t>(tid) < p.n_seqs) {         // one global read per sequence, all in flight together
-        const SeqDesc sd = seq_of(p, tid);
-        sn_all[tid] = sd.kv_hi - sd.kv_lo;
-        ss0_all[tid] = sd.kv_lo % ring;
-        sslot_all[tid] = sd.slot;
-    }
+    uint32_t* abase = cum + kPlanAbase;
+    uint32_t* sn_all = cum + kPlanSn;      // visible keys per sequence
+    uint32_t* ss0_all = cum + kPlanSs0;    // storage row of its first visible key
+    uint32_t* sslot_all = cum + kPlanSlot;
+    uint32_t* mode = cum + kPlanMode;      // [0] 1 = cell-aligned plan, [1] steps of the loop done (device plan only)
     // Two lanes: the first half of the grid walks sequences [0, lane_split), the second half the rest; each half
     // plans its own sequences with its own CTAs, and everything below indexes the lane's sequences from zero.
     const bool two_lanes = p.gather.lanes == 2;
@@ -151,22 +188,36 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     const uint32_t* sn = sn_all + seq_base;
     const uint32_t* ss0 = ss0_all + seq_base;
     const uint32_t* sslot = sslot_all + seq_base;
-    __syncthreads();
-    if (tid == 0) {
-        // cum[s] = tiles of all cells before (lane-local) sequence s
-        uint32_t c = 0;
-        for (uint32_t s = 0; s < n_seqs; ++s) {
-            cum[s] = c;
-            c += (sn[s] + kTileKeys - 1) / kTileKeys * HY;
+    const bool planned = p.plan_dev != nullptr;
+    if (planned) {
+        // The plan of the current positions was worked out by the kernel that advanced them: one coalesced read.
+        const uint32_t* src = p.plan_dev + (two_lanes ? 1u + glane : 0u) * kPlanWords;
+        for (int i = tid; i < kPlanWords; i += kDecodeThreads) cum[i] = __ldcg(src + i);
+        __syncthreads();
+    } else {
+        if (static_cast<uint32_t>(tid) < p.n_seqs) {  // one global read per sequence, all in flight together
+            const SeqDesc sd = seq_of(p, tid);
+            sn_all[tid] = sd.kv_hi - sd.kv_lo;
+            ss0_all[tid] = sd.kv_lo % ring;
+            sslot_all[tid] = sd.slot;
         }
-        cum[n_seqs] = c;
-        // The cell-aligned plan, if it costs at most a sixteenth more tiles per CTA than equal runs would.
-        const uint32_t total = c;
-        const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
-        uint32_t worst;
-        mode[0] = decode_aligned_plan(sn, n_seqs, HY, G, total, per, p.splits, abase, &worst) ? 1u : 0u;
+        __syncthreads();
+        if (tid == 0) {
+            // cum[s] = tiles of all cells before (lane-local) sequence s
+            uint32_t c = 0;
+            for (uint32_t s = 0; s < n_seqs; ++s) {
+                cum[s] = c;
+                c += (sn[s] + kTileKeys - 1) / kTileKeys * HY;
+            }
+            cum[n_seqs] = c;
+            // The cell-aligned plan, if it costs at most a sixteenth more tiles per CTA than equal runs would.
+            const uint32_t total = c;
+            const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
+            uint32_t worst;
+            mode[0] = decode_aligned_plan(sn, n_seqs, HY, G, total, per, p.splits, abase, &worst) ? 1u : 0u;
+        }
+        __syncthreads();
     }
-    __syncthreads();
     const uint32_t total = cum[n_seqs];
     const bool aligned = mode[0] != 0u;
     const uint32_t per = p.seq_dev ? (total + G - 1) / G : p.tiles_per_cta;
@@ -251,32 +302,49 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     // A layer's inputs exist only once every rank's heads of the previous layer have been gathered: check that the
     // peers' previous launch has arrived here.  The wait is bounded; if it runs out the kernel records that and
     // carries on (its own arithmetic does not depend on the gathered data).
-    // With two lanes the counters are the lane's own, and they also order everything this launch shares with the
-    // previous one (split scratch, tickets, accumulators of the lane's cells): the rank's own counter is among those
-    // polled, and a cell is announced only after its merge has read the scratch and reset its ticket.
+    // The counters are per sequence: a CTA waits only for the sequences it works on.  With two lanes they also
+    // order everything this launch shares with the previous one (split scratch, tickets, accumulators of those
+    // sequences' cells): the rank's own counter is among those polled, and a cell is announced only after its merge
+    // has read the scratch and reset its ticket.
     if (p.gather.n_peers != 0 && p.gather.wait_prev != 0) {
-        const uint32_t pollers = p.gather.n_peers + ((p.gather.stagger != 0 && glane == 1) ? 1u : 0u);
-        if (static_cast<uint32_t>(tid) < pollers) {  // one polling thread per source rank
-            const uint32_t steps_done = seq_of(p, 0).q_pos0 - *p.gather.base_pos;
-            const uint32_t launches_done = steps_done * p.gather.launches_per_step + p.gather.launches_before;
-            const unsigned int* arrived = p.gather.my_flags + glane * kMaxPeers + tid;
-            uint32_t target = launches_done * p.gather.lane_cells[glane];
-            if (static_cast<uint32_t>(tid) == p.gather.n_peers) {
-                // lane 1 of a step's first launch: hold back until this rank's lane 0 has delivered THIS launch
-                arrived = p.gather.my_flags + p.gather.my_rank;
-                target = (launches_done + 1) * p.gather.lane_cells[0];
-            }
+        int gave_up = 0;
+        if (p.gather.stagger_ns != 0 && glane == 1 && tid == 0) {
+            // lane 1 of a step's first launch: its first tiles are in flight; hold back before touching them
+            unsigned long long t0, t1;
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t0)::"memory");
+            do {
+                __nanosleep(200);
+                asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t1)::"memory");
+            } while (t1 - t0 < p.gather.stagger_ns);
+        }
+        // The sequences this CTA's run touches (one in the cell-aligned plan), one polling thread per (sequence,
+        // source rank).
+        uint32_t last_seq = my.seq;
+        if (!aligned) {
+            const uint64_t end = static_cast<uint64_t>(cta) * per + ntiles - 1;
+            while (last_seq + 1 < n_seqs && cum[last_seq + 1] <= end) ++last_seq;
+        }
+        const uint32_t n_polls = (last_seq - my.seq + 1) * p.gather.n_peers;
+        const uint32_t steps_done = planned ? mode[1] : seq_of(p, 0).q_pos0 - *p.gather.base_pos;
+        const uint32_t target = (steps_done * p.gather.launches_per_step + p.gather.launches_before) * p.gather.cells_per_seq;
+        for (uint32_t i = tid; i < n_polls; i += kDecodeThreads) {
+            const unsigned int* arrived =
+                p.gather.my_flags + (seq_base + my.seq + i / p.gather.n_peers) * kMaxPeers + i % p.gather.n_peers;
             uint32_t seen = 0, spins = 0;
             for (;;) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(arrived) : "memory");
                 if (seen >= target) break;
                 if (++spins > p.gather.poll_limit) {
                     atomicOr(p.gather.err, 1u);
+                    gave_up = 1;
                     break;
                 }
             }
         }
-        __syncthreads();
+        // A launch that orders itself by the counters alone must not go on without them: when a wait ran out (this
+        // rank's own counter may be among those still behind, held up by the previous launch's own waits), fall back
+        // to the stream order - the previous launch, whose every wait is bounded too, completes first.
+        if (__syncthreads_or(gave_up) != 0 && p.pdl == 3) pdl_wait();
         ITK_TRACE(p, 14);
     }
 
@@ -514,7 +582,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
             uint32_t n_parts = al_parts, part = al_part;
             if (!aligned) decode_cell_parts(cta, cum[cc.seq] + cc.hy * cc.T, cc.T, per, &n_parts, &part);
             finish_unit<kDecodeThreads, kDecodeMaxParts>(p, seq_base + cc.seq, cc.hy, n_parts, part, head0, nh, D, fo, fm,
-                                                         fl, flag, wscratch, glane);
+                                                         fl, flag, wscratch);
             fresh = true;
         }
         advance(cc);
@@ -611,9 +679,10 @@ cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t par
     return cudaGetLastError();
 }
 
-cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, uint64_t* launches) {
+cudaError_t launch_advance_states(SeqState* states, uint32_t n, uint32_t add, const DecodePlanSpec& spec, uint32_t* plan_out,
+                                  cudaStream_t s, uint64_t* launches) {
     if (!states || n == 0 || n > static_cast<uint32_t>(kMaxSeqsPerLaunch)) return cudaErrorInvalidValue;
-    advance_states_kernel<<<1, kMaxSeqsPerLaunch, 0, s>>>(states, n);
+    advance_states_kernel<<<1, kMaxSeqsPerLaunch, 0, s>>>(states, n, add, spec, plan_out);
     if (launches) *launches += 1;
     return cudaGetLastError();
 }

@@ -62,6 +62,7 @@ struct SlotState {
 };
 
 constexpr size_t kPartCellSplits = 148 * 64;  // (cell, split) partials the scratch holds
+constexpr size_t kGatherHeader = 4096, kGatherErr = 2048, kGatherBase = 2176;  // layout of a gather buffer's header
 
 }  // namespace
 
@@ -122,8 +123,14 @@ struct itk_backend {
     // two-lane schedule of the loop's gathering launches (see GatherTarget): 1 = off
     uint32_t res_lanes = 1, res_lane_split = 0, res_lane_ctas = 0;
     int lanes_mode = 1;        // option decode_lanes: 0 = never, 1 = when a launch is short enough to gain, 2 = whenever possible
-    bool lane_stagger = true;  // option decode_lane_stagger: lane 1 of a step's first launch starts behind lane 0
-    // fused gather: one allocation per rank = [256-byte header: flags[8], err @64, base_pos @128][data]
+    int lane_stagger = 100;    // option decode_lane_stagger: how far lane 1 of a step's first launch starts behind lane 0,
+                               // in per cent of the time lane 0 needs to stream its keys (0 = together)
+    uint64_t res_lane0_tiles = 0;  // 64-key tiles of lane 0 in one launch when the loop began
+    uint32_t* d_plan = nullptr;  // the decode kernel's work plan of the loop's current positions (device words)
+    itk::DecodePlanSpec res_spec{};
+    bool res_planned = false;    // the plan is kept on the device (all layers global)
+    // fused gather: one allocation per rank = [kGatherHeader bytes: arrival counters [64 sequences][8 ranks], status word
+    // @kGatherErr, loop base position @kGatherBase][data]
     unsigned char* gth_local = nullptr;
     unsigned char* gth_peer[itk::kMaxPeers] = {};
     bool gth_attached[itk::kMaxPeers] = {};  // the caller's mapping (itk_gather_attach): not closed by the backend
@@ -677,6 +684,8 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (e != cudaSuccess) return cuda_refuse(e, "staging allocation");
     e = cudaMalloc(&b->d_states, itk::kMaxSeqsPerLaunch * sizeof(itk::SeqState));
     if (e != cudaSuccess) return cuda_refuse(e, "sequence-state allocation");
+    e = cudaMalloc(&b->d_plan, (itk::kDecodePlanBlocks * itk::kDecodePlanWords + 4) * sizeof(uint32_t));
+    if (e != cudaSuccess) return cuda_refuse(e, "plan allocation");
     e = cudaMalloc(&b->d_status, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMallocHost(&b->h_status, sizeof(unsigned int));
     if (e != cudaSuccess) return cuda_refuse(e, "status word allocation");
@@ -715,6 +724,7 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->d_out);
     cudaFree(b->gather_buf);
     cudaFree(b->d_states);
+    cudaFree(b->d_plan);
     cudaFree(b->d_status);
     if (b->h_status) cudaFreeHost(b->h_status);
     for (uint32_t j = 0; j < itk::kMaxPeers; ++j)
@@ -760,7 +770,11 @@ int itk_set_option(itk_backend* b, const char* name, int64_t value) {
         b->lanes_mode = static_cast<int>(value);
         return ITK_OK;
     }
-    if (key == "decode_lane_stagger") return flag(&b->lane_stagger);
+    if (key == "decode_lane_stagger") {
+        if (value < 0 || value > 400) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: decode_lane_stagger is 0..400 (per cent)");
+        b->lane_stagger = static_cast<int>(value);
+        return ITK_OK;
+    }
     if (key == "pdl") return flag(&b->use_pdl);
     if (key == "decode_fused_sum") return flag(&b->fused_sum);
     if (key == "separate_append") return flag(&b->separate_append);
@@ -967,10 +981,27 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
                      itk::decode_parts_for(static_cast<uint32_t>(te), pe) <= cap &&
                      itk::decode_parts_for(static_cast<uint32_t>(te), ps) <= cap;
             }
-        if (ok) lanes = 2;
+        if (ok) {
+            lanes = 2;
+            lane_tiles(0, 0, lane_split, 0, &tm, &b->res_lane0_tiles);
+        }
     }
+    // The plan of the current positions lives on the device (worked out by the kernel that moves the positions) when
+    // every layer sees the same keys, i.e. all layers are global; otherwise every CTA derives its own.
+    bool all_global = true;
+    for (uint32_t l = 0; l < b->cfg.n_layers; ++l) all_global = all_global && b->window[l] == 0;
+    b->res_planned = all_global;
+    b->res_spec.cells_per_seq = HY;
+    b->res_spec.ctas = static_cast<uint32_t>(ctas);
+    b->res_spec.lane_ctas = lanes == 2 ? lane_ctas : 0u;
+    b->res_spec.lane_split = lane_split;
+    b->res_spec.splits = static_cast<uint32_t>(cap);
     ITK_CUDA(b, cudaMemcpyAsync(b->d_states, states.data(), n_seqs * sizeof(itk::SeqState), cudaMemcpyHostToDevice,
                                 b->stream), "sequence-state upload");
+    ITK_CUDA(b, cudaMemcpyAsync(b->d_plan + itk::kDecodePlanBlocks * itk::kDecodePlanWords, &states[0].pos, sizeof(uint32_t),
+                                cudaMemcpyHostToDevice, b->stream), "loop base position upload");
+    ITK_CUDA(b, itk::launch_advance_states(b->d_states, n_seqs, 0, b->res_spec, all_global ? b->d_plan : nullptr, b->stream,
+                                           &b->stats.kernel_launches), "plan launch");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
 #ifdef ITK_DECODE_TRACE
     if (!g_trace) {  // timeline build: allocate before any capture begins; the caller reads it back through
@@ -990,7 +1021,7 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
     b->res_prev_layer = -1;
     b->res_launches_in_step = 0;
     if (b->gth_local) {
-        ITK_CUDA(b, cudaMemcpyAsync(b->gth_local + 128, &states[0].pos, sizeof(uint32_t), cudaMemcpyHostToDevice, b->stream),
+        ITK_CUDA(b, cudaMemcpyAsync(b->gth_local + kGatherBase, &states[0].pos, sizeof(uint32_t), cudaMemcpyHostToDevice, b->stream),
                  "gather base position upload");
         ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather base position upload");
     }
@@ -1031,6 +1062,7 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
     p.k_new = d_k;
     p.v_new = d_v;
     p.seq_dev = b->d_states;
+    p.plan_dev = b->res_planned ? b->d_plan : nullptr;
     if (b->fused_sum) {
         p.acc_o = b->acc_o;
         p.acc_l = b->acc_l;
@@ -1049,21 +1081,26 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
         p.gather.my_rank = b->gth_rank;
         for (uint32_t j = 0; j < b->gth_world; ++j) {
             if (!b->gth_peer[j]) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: rank " + zu(j) + " is not open");
-            p.gather.peer_out[j] = reinterpret_cast<float*>(b->gth_peer[j] + 256 + gather_offset_bytes);
+            p.gather.peer_out[j] = reinterpret_cast<float*>(b->gth_peer[j] + kGatherHeader + gather_offset_bytes);
             p.gather.peer_flags[j] = reinterpret_cast<unsigned int*>(b->gth_peer[j]);
         }
         p.gather.my_flags = reinterpret_cast<const unsigned int*>(b->gth_local);
-        p.gather.err = reinterpret_cast<unsigned int*>(b->gth_local + 64);
-        p.gather.base_pos = reinterpret_cast<const uint32_t*>(b->gth_local + 128);
+        p.gather.err = reinterpret_cast<unsigned int*>(b->gth_local + kGatherErr);
+        p.gather.base_pos = reinterpret_cast<const uint32_t*>(b->gth_local + kGatherBase);
         p.gather.launches_per_step = b->cfg.n_layers;
         p.gather.launches_before = b->res_launches_in_step;
         const uint32_t HY = b->cfg.kv_heads * b->gchunks;
         two_lanes = b->res_lanes == 2;
         p.gather.lanes = two_lanes ? 2u : 1u;
         p.gather.lane_split = two_lanes ? b->res_lane_split : 0u;
-        p.gather.lane_cells[0] = (two_lanes ? b->res_lane_split : p.n_seqs) * HY;
-        p.gather.lane_cells[1] = two_lanes ? (p.n_seqs - b->res_lane_split) * HY : 0u;
-        p.gather.stagger = (two_lanes && b->lane_stagger && b->use_pdl && b->res_launches_in_step == 0) ? 1u : 0u;
+        p.gather.cells_per_seq = HY;
+        p.gather.stagger_ns = 0;
+        if (two_lanes && b->lane_stagger > 0 && b->use_pdl && b->res_launches_in_step == 0) {
+            // what lane 0 needs to stream its keys once, at about 6.5 TB/s = 6500 bytes per nanosecond
+            const double lane0_bytes = static_cast<double>(b->res_lane0_tiles) * 64.0 * b->cfg.head_dim * 2.0 * 2.0;
+            p.gather.stagger_ns = static_cast<uint32_t>(lane0_bytes / 6500.0 * b->lane_stagger / 100.0);
+            if (p.gather.stagger_ns > 200000u) p.gather.stagger_ns = 200000u;
+        }
         p.gather.wait_prev = 1u;
         p.gather.poll_limit = b->gth_poll_limit;
     }
@@ -1101,8 +1138,8 @@ int itk_gather_create(itk_backend* b, uint32_t world, uint32_t rank, uint64_t da
         return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: 1..8 ranks, rank < world, non-empty buffer");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
     void* ptr = nullptr;
-    ITK_CUDA(b, cudaMalloc(&ptr, 256 + data_bytes), "gather buffer allocation");
-    ITK_CUDA(b, cudaMemset(ptr, 0, 256 + data_bytes), "gather buffer clear");
+    ITK_CUDA(b, cudaMalloc(&ptr, kGatherHeader + data_bytes), "gather buffer allocation");
+    ITK_CUDA(b, cudaMemset(ptr, 0, kGatherHeader + data_bytes), "gather buffer clear");
     cudaIpcMemHandle_t h;
     cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
     if (e != cudaSuccess) {
@@ -1115,7 +1152,7 @@ int itk_gather_create(itk_backend* b, uint32_t world, uint32_t rank, uint64_t da
     b->gth_rank = rank;
     b->gth_bytes = data_bytes;
     b->gth_peer[rank] = b->gth_local;
-    *local_data = b->gth_local + 256;
+    *local_data = b->gth_local + kGatherHeader;
     return ITK_OK;
 }
 
@@ -1139,8 +1176,22 @@ int itk_gather_attach(itk_backend* b, uint32_t peer_rank, void* peer_local_data)
         return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: create the local buffer first; rank must be < world");
     if (peer_rank == b->gth_rank) return ITK_OK;
     if (b->gth_peer[peer_rank]) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: rank " + zu(peer_rank) + " is already open");
-    b->gth_peer[peer_rank] = static_cast<unsigned char*>(peer_local_data) - 256;  // the header sits before the data
+    b->gth_peer[peer_rank] = static_cast<unsigned char*>(peer_local_data) - kGatherHeader;  // the header sits before the data
     b->gth_attached[peer_rank] = true;
+    return ITK_OK;
+}
+
+int itk_gather_close_peers(itk_backend* b) {
+    if (!b) return ITK_ERR_INVALID_ARGUMENT;
+    cudaSetDevice(b->cfg.device);
+    if (b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: end the resident loop first");
+    if (b->stream) ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather close");
+    for (uint32_t j = 0; j < itk::kMaxPeers; ++j) {
+        if (j == b->gth_rank || !b->gth_peer[j]) continue;
+        if (!b->gth_attached[j]) cudaIpcCloseMemHandle(b->gth_peer[j]);
+        b->gth_peer[j] = nullptr;
+        b->gth_attached[j] = false;
+    }
     return ITK_OK;
 }
 
@@ -1148,7 +1199,7 @@ int itk_gather_reset(itk_backend* b) {
     if (!b) return ITK_ERR_INVALID_ARGUMENT;
     cudaSetDevice(b->cfg.device);
     if (!b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: no gather buffer");
-    ITK_CUDA(b, cudaMemsetAsync(b->gth_local, 0, 128, b->stream), "gather flag clear");
+    ITK_CUDA(b, cudaMemsetAsync(b->gth_local, 0, kGatherErr + 64, b->stream), "gather flag clear");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather flag clear");
     return ITK_OK;
 }
@@ -1158,15 +1209,16 @@ int itk_gather_status(itk_backend* b, uint32_t* error_bits) {
     cudaSetDevice(b->cfg.device);
     if (!b->gth_local) return b->fail(ITK_ERR_INVALID_ARGUMENT, "fused gather: no gather buffer");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "gather status");
-    ITK_CUDA(b, cudaMemcpy(error_bits, b->gth_local + 64, sizeof(uint32_t), cudaMemcpyDeviceToHost), "gather status");
+    ITK_CUDA(b, cudaMemcpy(error_bits, b->gth_local + kGatherErr, sizeof(uint32_t), cudaMemcpyDeviceToHost), "gather status");
     return ITK_OK;
 }
 
 int itk_resident_advance(itk_backend* b) {
     if (!b) return ITK_ERR_INVALID_ARGUMENT;
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
-    ITK_CUDA(b, itk::launch_advance_states(b->d_states, static_cast<uint32_t>(b->res_slots.size()), b->stream,
-                                           &b->stats.kernel_launches), "state advance launch");
+    ITK_CUDA(b, itk::launch_advance_states(b->d_states, static_cast<uint32_t>(b->res_slots.size()), 1, b->res_spec,
+                                           b->res_planned ? b->d_plan : nullptr, b->stream, &b->stats.kernel_launches),
+             "state advance launch");
     b->res_prev_layer = -1;
     b->res_launches_in_step = 0;
     return ITK_OK;

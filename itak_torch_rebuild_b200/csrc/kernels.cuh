@@ -54,19 +54,19 @@ constexpr int kMaxPeers = 8;  // GPUs of one box
 
 // The per-layer gather of head outputs done by the decode kernel itself: the CTA that writes a cell's final
 // output stores it into the same place of every rank's gather buffer (plain stores to peer-mapped memory over
-// NVLink) and then bumps entry [lane][my_rank] of every rank's flag array, so a consumer on rank j knows that rank r
-// has delivered c cells of a lane once flags_j[lane][r] >= c.
+// NVLink) and then bumps entry [sequence][my_rank] of every rank's counter array, so a consumer on rank j knows that
+// rank r has delivered c cells of a sequence (cells_per_seq per launch) once counters_j[sequence][r] >= c.
 //
 // Lanes.  A layer's inputs for one sequence depend on the previous layer's gathered outputs of THAT sequence only, so
 // the batch can run as two halves ("lanes": sequences [0, lane_split) and [lane_split, n_seqs)) that are out of phase
 // with each other: while one lane's outputs cross NVLink and the next layer waits for them, the other lane streams
 // its cache.  With lanes == 2 the first half of the grid's CTAs serves lane 0 and the second half lane 1 (one CTA of
-// each per SM), every lane has its own arrival counters, and a CTA waits for its own lane's previous launch only.
+// each per SM), and a CTA waits only for the previous launch's cells of the sequences it works on itself.
 struct GatherTarget {
     uint32_t n_peers;                    // 0 = outputs go to AttnLaunch::out only
     uint32_t my_rank;
     float* peer_out[kMaxPeers];          // this rank's [n_seqs][q_heads][D] slot inside every rank's buffer
-    unsigned int* peer_flags[kMaxPeers]; // every rank's flag array ([2 lanes][kMaxPeers] entries)
+    unsigned int* peer_flags[kMaxPeers]; // every rank's counter array ([kMaxSeqsPerLaunch][kMaxPeers] entries)
     const unsigned int* my_flags;        // the local flag array, written by the peers
     unsigned int* err;                   // local word: bit 0 = a bounded wait ran out
     const uint32_t* base_pos;            // device word: position of sequence 0 when the loop began
@@ -74,9 +74,10 @@ struct GatherTarget {
     uint32_t launches_before;            // decode launches of this step that precede this one
     uint32_t lanes;                      // 1, or 2 = the two-lane schedule described above
     uint32_t lane_split;                 // first sequence of lane 1
-    uint32_t lane_cells[2];              // cells every rank delivers per launch, per lane (lane 0 = all when lanes == 1)
-    uint32_t stagger;                    // 1 = (first launch of a step, two lanes) lane 1 starts once lane 0's cells of
-                                         // this launch are out on this rank, which puts the lanes out of phase
+    uint32_t cells_per_seq;              // cells every rank delivers per sequence and launch
+    uint32_t stagger_ns;                 // (first launch of a step, two lanes) lane 1 holds back this long after its
+                                         // CTAs start - about half of what a lane takes to stream - which puts the two
+                                         // lanes out of phase for the rest of the step; 0 = no hold
     uint32_t wait_prev;                  // 1 = before using its inputs, check that every peer's previous launch arrived
     uint32_t poll_limit;                 // polls of one arrival flag before the wait gives up and records that
 };
@@ -112,6 +113,9 @@ struct AttnLaunch {
     GatherTarget gather;     // decode kernel (replayable loop): fused all-gather of the outputs
     const SeqState* seq_dev; // decode kernel: when set, sequences come from device memory instead of `seq`, and
                              // tiles_per_cta is derived in the kernel from the grid size
+    const uint32_t* plan_dev; // decode kernel, with seq_dev: the work plan of the current positions, worked out once
+                             // per step by the kernel that advances them (kDecodePlanBlocks blocks of kDecodePlanWords
+                             // words: whole batch, lane 0, lane 1); null = every CTA works it out itself
     unsigned int* status;    // device word the kernels OR error bits into (bit 0: a bounded wait on the tensor
                              // core ran out in the tcgen05 multi-row kernel); may be null
     float scale;             // score scale, 1/sqrt(D) by default
@@ -202,8 +206,22 @@ constexpr uint32_t kDecodeMaxParts = 64;
 cudaError_t launch_decode_f16_resident(AttnLaunch p, uint32_t ctas, uint32_t parts_stride, cudaStream_t s,
                                        uint64_t* launches);
 // pdl != 0 launches with programmatic stream serialization (see AttnLaunch::pdl).
-// pos += 1 for the first n states.
-cudaError_t launch_advance_states(SeqState* states, uint32_t n, cudaStream_t s, uint64_t* launches);
+// The decode kernel's work plan as device words (AttnLaunch::plan_dev): per block the running tile counts, the
+// aligned plan's first CTAs, every sequence's visible keys / first storage row / slot, and [mode, steps done].
+constexpr int kDecodePlanWords = 2 * (kMaxSeqsPerLaunch + 4) + 3 * kMaxSeqsPerLaunch + 4;
+constexpr int kDecodePlanBlocks = 3;  // 0 = the whole batch on `ctas` CTAs, 1 and 2 = the lanes on lane_ctas / 2 each
+struct DecodePlanSpec {
+    uint32_t cells_per_seq;  // KV heads x head chunks
+    uint32_t ctas;           // CTAs of a launch without lanes
+    uint32_t lane_ctas;      // CTAs of a two-lane launch (both lanes), 0 = no lanes
+    uint32_t lane_split;     // first sequence of lane 1
+    uint32_t splits;         // partial slots per cell
+};
+// (behind the blocks, plan_out holds one more word: the position of sequence 0 when the loop began, written by the host)
+// pos += add for the first n states (global layers only: a sequence sees positions 0..pos), then the plans of the new
+// positions into plan_out (may be null: positions only).
+cudaError_t launch_advance_states(SeqState* states, uint32_t n, uint32_t add, const DecodePlanSpec& spec, uint32_t* plan_out,
+                                  cudaStream_t s, uint64_t* launches);
 // The decode kernel's cell-aligned plan: every cell (sequence s has `cells_per_seq` of them, each of
 // tiles(keys[s]) 64-key tiles) gets floor(G * T / total) CTAs of its own and equal runs inside it.  Returns
 // whether that plan is taken - every cell gets at least one CTA, no cell needs more than `splits` parts and the

@@ -1,6 +1,7 @@
 """The all-gather fused into the decode kernel, on 2 GPUs: each rank holds half of the KV heads, runs the replayable
-loop with itk_resident_layer_gather, and every rank's gather buffer must end up holding every rank's head outputs -
-the same values an NCCL all-gather of the ordinary per-rank outputs delivers.  Needs two GPUs; skipped otherwise."""
+loop with itk_resident_layer_gather - with and without the two-lane schedule - and every rank's gather buffer must
+end up holding every rank's head outputs: the same values an NCCL all-gather of the ordinary per-rank outputs
+delivers.  Needs two GPUs; skipped otherwise."""
 import os
 import socket
 import sys
@@ -22,7 +23,7 @@ class _DevArray:
         self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
 
 
-def _worker(rank, world, port, use_graph, result):
+def _worker(rank, world, port, use_graph, lanes, result):
     import torch
     import torch.distributed as dist
 
@@ -38,7 +39,7 @@ def _worker(rank, world, port, use_graph, result):
     n = len(lens)
     sh = sharding.plan(hq, hkv, n, rank, world)
     a = CudaCompute(layers, sh.q_heads, sh.kv_heads, d, n_slots=n, max_context=400, chunk_cap=1, kv_dtype=KvDtype.F16,
-                    device=rank)  # fused loop
+                    device=rank, options={"decode_lanes": lanes})  # fused loop
     b = CudaCompute(layers, sh.q_heads, sh.kv_heads, d, n_slots=n, max_context=400, chunk_cap=1, kv_dtype=KvDtype.F16,
                     device=rank)  # ordinary calls
     rng = np.random.default_rng(4)  # every rank draws the same global tensors and keeps its heads
@@ -116,8 +117,9 @@ def _worker(rank, world, port, use_graph, result):
     os._exit(0)
 
 
+@pytest.mark.parametrize("lanes", [0, 2])
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_fused_gather_matches_nccl_all_gather(use_graph):
+def test_fused_gather_matches_nccl_all_gather(use_graph, lanes):
     import torch
     import torch.multiprocessing as mp
 
@@ -128,7 +130,7 @@ def test_fused_gather_matches_nccl_all_gather(use_graph):
         port = sock.getsockname()[1]
     ctx = mp.get_context("spawn")
     result = ctx.SimpleQueue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, use_graph, result)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, use_graph, lanes, result)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
