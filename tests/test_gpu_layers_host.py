@@ -43,10 +43,10 @@ def test_one_call_per_forward_equals_one_call_per_layer(dtype, d, rows):
             per_layer = b.attention_batch(layer, slots, pos, rows, q[layer], k[layer], v[layer]).reshape(n, rows, hq * d)
             assert got[layer].tobytes() == per_layer.tobytes(), f"layer {layer}: differs from the per-layer call"
             for slot in range(n):
-                refs[slot].append_rows(layer, stored(k[layer, slot], dtype), stored(v[layer, slot], dtype), pos[slot])
-                want = orc.gqa_attention(q[layer, slot], rows, hq, list(range(pos[slot], pos[slot] + rows)),
-                                         refs[slot].view(layer))
-                assert_attention_close(got[layer, slot], want, hq, d, dtype, f"layer {layer} slot {slot}")
+                for r in range(rows):  # the reference's order: append a row, attend it (a ring layer evicts as it goes)
+                    refs[slot].append(layer, stored(k[layer, slot, r], dtype), stored(v[layer, slot, r], dtype), pos[slot] + r)
+                    want = orc.gqa_attention(q[layer, slot, r], 1, hq, [pos[slot] + r], refs[slot].view(layer))
+                    assert_attention_close(got[layer, slot, r], want, hq, d, dtype, f"layer {layer} slot {slot} row {r}")
         pos = [p + rows for p in pos]
     for slot in range(n):
         for layer in range(layers):
