@@ -85,8 +85,11 @@ __device__ __forceinline__ void signal_cell_delivered(const AttnLaunch& p, uint3
     // (no value comes back, so nothing waits for another NVLink round trip).
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
-        ITK_TRACE(p, 15);  // (timeline build) the system-scope fence has returned
+        if (p.gather.local_only != 0)
+            __threadfence();
+        else
+            __threadfence_system();
+        ITK_TRACE(p, 15);  // (timeline build) the fence has returned
         for (uint32_t j = 0; j < p.gather.n_peers; ++j)
             asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;\n" ::"l"(p.gather.peer_flags[j] + unit * kMaxPeers + p.gather.my_rank) : "memory");
     }

@@ -126,6 +126,7 @@ struct itk_backend {
     int lane_stagger = 100;    // option decode_lane_stagger: how far lane 1 of a step's first launch starts behind lane 0,
                                // in per cent of the time lane 0 needs to stream its keys (0 = together)
     uint64_t res_lane0_tiles = 0;  // 64-key tiles of lane 0 in one launch when the loop began
+    unsigned char* lane_hdr = nullptr;  // arrival counters of a single-GPU loop run in lanes (a gather header without data)
     uint32_t* d_plan = nullptr;  // the decode kernel's work plan of the loop's current positions (device words)
     itk::DecodePlanSpec res_spec{};
     bool res_planned = false;    // the plan is kept on the device (all layers global)
@@ -686,6 +687,9 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     if (e != cudaSuccess) return cuda_refuse(e, "sequence-state allocation");
     e = cudaMalloc(&b->d_plan, (itk::kDecodePlanBlocks * itk::kDecodePlanWords + 4) * sizeof(uint32_t));
     if (e != cudaSuccess) return cuda_refuse(e, "plan allocation");
+    e = cudaMalloc(&b->lane_hdr, kGatherHeader);
+    if (e != cudaSuccess) return cuda_refuse(e, "lane counter allocation");
+    cudaMemsetAsync(b->lane_hdr, 0, kGatherHeader, b->stream);
     e = cudaMalloc(&b->d_status, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMallocHost(&b->h_status, sizeof(unsigned int));
     if (e != cudaSuccess) return cuda_refuse(e, "status word allocation");
@@ -725,6 +729,7 @@ void itk_backend_destroy(itk_backend* b) {
     cudaFree(b->gather_buf);
     cudaFree(b->d_states);
     cudaFree(b->d_plan);
+    cudaFree(b->lane_hdr);
     cudaFree(b->d_status);
     if (b->h_status) cudaFreeHost(b->h_status);
     for (uint32_t j = 0; j < itk::kMaxPeers; ++j)
@@ -1000,6 +1005,11 @@ int itk_resident_begin(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, u
                                 b->stream), "sequence-state upload");
     ITK_CUDA(b, cudaMemcpyAsync(b->d_plan + itk::kDecodePlanBlocks * itk::kDecodePlanWords, &states[0].pos, sizeof(uint32_t),
                                 cudaMemcpyHostToDevice, b->stream), "loop base position upload");
+    if (lanes == 2) {  // the counters a single-GPU loop's lanes order themselves by start from zero with the loop
+        ITK_CUDA(b, cudaMemsetAsync(b->lane_hdr, 0, kGatherErr + 64, b->stream), "lane counter clear");
+        ITK_CUDA(b, cudaMemcpyAsync(b->lane_hdr + kGatherBase, &states[0].pos, sizeof(uint32_t), cudaMemcpyHostToDevice,
+                                    b->stream), "loop base position upload");
+    }
     ITK_CUDA(b, itk::launch_advance_states(b->d_states, n_seqs, 0, b->res_spec, all_global ? b->d_plan : nullptr, b->stream,
                                            &b->stats.kernel_launches), "plan launch");
     ITK_CUDA(b, cudaStreamSynchronize(b->stream), "sequence-state upload");
@@ -1087,6 +1097,20 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
         p.gather.my_flags = reinterpret_cast<const unsigned int*>(b->gth_local);
         p.gather.err = reinterpret_cast<unsigned int*>(b->gth_local + kGatherErr);
         p.gather.base_pos = reinterpret_cast<const uint32_t*>(b->gth_local + kGatherBase);
+    } else if (b->res_lanes == 2 && b->use_pdl) {
+        // A single-GPU loop on a short launch runs in lanes too: the outputs go to the caller's buffer through the
+        // gather's store path with this GPU as the only rank, and the arrival counters are the backend's own.
+        p.out = nullptr;
+        p.gather.n_peers = 1;
+        p.gather.my_rank = 0;
+        p.gather.local_only = 1;
+        p.gather.peer_out[0] = d_out;
+        p.gather.peer_flags[0] = reinterpret_cast<unsigned int*>(b->lane_hdr);
+        p.gather.my_flags = reinterpret_cast<const unsigned int*>(b->lane_hdr);
+        p.gather.err = reinterpret_cast<unsigned int*>(b->lane_hdr + kGatherErr);
+        p.gather.base_pos = reinterpret_cast<const uint32_t*>(b->lane_hdr + kGatherBase);
+    }
+    if (p.gather.n_peers != 0) {
         p.gather.launches_per_step = b->cfg.n_layers;
         p.gather.launches_before = b->res_launches_in_step;
         const uint32_t HY = b->cfg.kv_heads * b->gchunks;

@@ -79,6 +79,8 @@ struct GatherTarget {
                                          // CTAs start - about half of what a lane takes to stream - which puts the two
                                          // lanes out of phase for the rest of the step; 0 = no hold
     uint32_t wait_prev;                  // 1 = before using its inputs, check that every peer's previous launch arrived
+    uint32_t local_only;                 // 1 = the only "peer" is this GPU itself (a single-GPU loop run in lanes): the
+                                         // outputs and counters need device scope only
     uint32_t poll_limit;                 // polls of one arrival flag before the wait gives up and records that
 };
 
