@@ -121,8 +121,18 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar_addr, uint32_t parity
         if ((p).trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (slot) < 512)         \
             (p).trace[(slot)] = static_cast<unsigned long long>(clock64());                            \
     } while (0)
+// ... and four wall-clock stamps of every CTA: entry, first scores issued, last value product complete, exit.
+#define TC_STAMP(p, i)                                                                                         \
+    do {                                                                                                       \
+        if ((p).trace) {                                                                                       \
+            unsigned long long t_;                                                                             \
+            asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t_)::"memory");                                 \
+            (p).trace[1024 + ((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 4 + (i)] = t_;  \
+        }                                                                                                      \
+    } while (0)
 #else
 #define TC_TRACE(p, slot) do { } while (0)
+#define TC_STAMP(p, i) do { } while (0)
 #endif
 
 // PC = pairs per CTA (32 or 64).
@@ -178,28 +188,34 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t ntiles = (span + kTcTile - 1) / kTcTile;
 
     if (tid == 0) TC_TRACE(p, 256);
+    if (tid == 0) TC_STAMP(p, 0);
     // Launched as a programmatic dependent of the previous kernel in the stream (AttnLaunch::pdl): this grid's CTAs are
     // placed as SMs free up instead of after the previous grid has drained and a launch has crossed the bus; nothing
     // is read or written before the previous kernel's memory is visible.
-    if (p.pdl != 0) {
-        asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-        asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    }
+    // pdl 1: wait for the predecessor, and only then let this grid's own dependents start (they may rely on what this
+    // one waited for).  pdl 2 (the predecessor is another layer's launch of this kernel, and so is everything that
+    // can still be running): the K/V loaders start streaming this layer's stored rows at once - nothing in flight
+    // writes them - while every thread that touches the queries, the call's new rows, the scratch or the outputs
+    // waits first.
+    const bool early_kv = p.pdl == 2;
+    if (p.pdl == 1) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (p.pdl != 0) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // The query rows are requested first of all (each softmax warp a quarter of the CTA's PC distinct rows, lane l
     // the 16-byte chunk l of a row), so that their latency runs underneath the set-up below instead of behind the
-    // opening burst of K/V tile loads.
+    // opening burst of K/V tile loads.  (An early launch requests them once it has waited, after the set-up.)
     float4 q_ld[PC / 4];
-    if (warp < kTcMmaWarp) {
+    auto request_queries = [&]() {
 #pragma unroll
         for (int rr = 0; rr < PC / 4; ++rr) {
             const uint32_t spair = pc * PC + warp * (PC / 4) + rr;
             q_ld[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (spair < n_pairs)
-                q_ld[rr] = __ldg(reinterpret_cast<const float4*>(
-                                     p.q + ((static_cast<size_t>(seq) * p.rows + spair / nh) * p.q_heads + head0 + spair % nh) *
-                                               kTcD) + lane);
+                q_ld[rr] = __ldcg(reinterpret_cast<const float4*>(
+                                      p.q + ((static_cast<size_t>(seq) * p.rows + spair / nh) * p.q_heads + head0 + spair % nh) *
+                                                kTcD) + lane);
         }
-    }
+    };
+    if (warp < kTcMmaWarp && !early_kv) request_queries();
     if (tid == 0) {
         for (int s = 0; s < kTcStagesK; ++s) {
             tc::mbar_init(bar_full_k + 8 * s, kTcLoaderThreads);
@@ -228,6 +244,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = *slot_ptr;
+    if (early_kv && warp < kTcMmaWarp) {
+        // Early launch: the barriers and tensor memory are set up and the loaders are already streaming; clear the
+        // weight buffers while the predecessor finishes, then wait for it and only then touch the queries.
+        uint32_t z[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) z[j] = 0u;
+#pragma unroll 1
+        for (int c = 0; c < kTcTile; c += 16) tc::tmem_st16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + kTmemP + c, z);
+        tc::tmem_wait_st();
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        request_queries();
+    }
 
     if (warp > kTcMmaWarp && warp < kTcPvWarp) {
         // ---------------- loaders: warp 5 streams K, warp 6 streams V; thread lt copies 16-byte chunk c of rows
@@ -250,6 +278,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         const int64_t new_rel = static_cast<int64_t>(sd.q_pos0) - (static_cast<int64_t>(sd.kv_lo) + k0);
         // the CTAs of the LAST pair block see every row of the launch: they are the ones that store them
         const bool stores_new = gc == 0 && pc == pchunks - 1;
+        bool waited = !early_kv;  // (early start) has this loader thread waited for the predecessor yet
+        // Before the query rows have left their staging area (the last V stage): an ordinary launch requests only the
+        // first K tile (see below); an early one fills the K ring and all V stages but the last.
+        const uint32_t go_tile = early_kv ? (is_v ? static_cast<uint32_t>(kTcStagesV - 1) : 0xffffffffu) : (is_v ? 0u : 1u);
         for (uint32_t tile = 0; tile < ntiles; ++tile) {
             if (*abort_flag != 0) break;
             const uint32_t st = tile % nst;
@@ -264,6 +296,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             constexpr int kPre = 4;
             float4 pre[kPre][2];
             int pre_i0 = 0;
+            if (has_new && !waited) {  // the call's new rows come from the caller, and this thread may store them
+                asm volatile("griddepcontrol.wait;\n" ::: "memory");
+                waited = true;
+            }
             if (has_new) {
                 const int64_t first = new_rel - static_cast<int64_t>(row0) - rg;  // row index (rg + 2i) of the first new row
                 pre_i0 = first > 0 ? static_cast<int>((first + 1) / 2) : 0;
@@ -278,7 +314,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                     }
                 }
             }
-            if (tile == (is_v ? 0u : 1u) && !wait_or_abort(bar_go, 0u, abort_flag)) break;
+            if (tile == go_tile && !wait_or_abort(bar_go, 0u, abort_flag)) break;
             if (tile >= nst && !wait_or_abort(bar_empty + 8 * st, (tile / nst - 1) & 1u, abort_flag)) break;
             const uint32_t dst = buf + st * kStageBytes;
             if (has_new) {
@@ -396,6 +432,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                     tc::fence_proxy_async();  // the tile was written through the generic proxy (cp.async)
                     tc::fence_after_sync();
                     TC_TRACE(p, tile * 8 + 0);
+                    if (tile == 0) TC_STAMP(p, 1);
                     const uint32_t kst = kbuf + (tile % kTcStagesK) * kStageBytes;
 #pragma unroll
                     for (int ks = 0; ks < 16; ++ks)  // 16 halfs of the contraction per MMA
@@ -492,12 +529,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             }
             if (tid == 0) TC_TRACE(p, 257);
             mbar_arrive(bar_go);  // (release) the staging area may be overwritten by the V stream
-            // Both P buffers start as zeros: a row only ever writes its own columns.
-            uint32_t z[16];
+            // Both P buffers start as zeros: a row only ever writes its own columns (an early launch cleared them
+            // while it waited).
+            if (!early_kv) {
+                uint32_t z[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) z[j] = 0u;
+                for (int j = 0; j < 16; ++j) z[j] = 0u;
 #pragma unroll 1
-            for (int c = 0; c < kTcTile; c += 16) tc::tmem_st16(tmem + lane_base + kTmemP + c, z);
+                for (int c = 0; c < kTcTile; c += 16) tc::tmem_st16(tmem + lane_base + kTmemP + c, z);
+            }
             tc::tmem_wait_st();
             tc::fence_before_sync();
             mbar_arrive(bar_q);
@@ -621,6 +661,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         if (done)
             done = __all_sync(0xffffffffu, wait_or_abort(bar_o + 8 * ((ntiles - 1) & 1u), ((ntiles - 1) >> 1) & 1u, abort_flag));
         tc::fence_after_sync();
+        if (tid == 0) TC_STAMP(p, 2);
         const bool have_o = done;
         if (x != 0u) l = 0.f;  // the hi and lo rows of a pair saw the same weights: their sum counts once
         softmax_sync();  // the rings are idle now (every tile was consumed): they become staging space
@@ -744,6 +785,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     tc::fence_before_sync();
     __syncthreads();
     if (tid == 0) TC_TRACE(p, 258);
+    if (tid == 0) TC_STAMP(p, 3);
     if (tid == 0 && *abort_flag != 0 && p.status) atomicOr(p.status, 1u);
     if (warp == kTcMmaWarp) tc::tmem_dealloc(tmem, kTmemCols);
 }

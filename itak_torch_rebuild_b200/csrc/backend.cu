@@ -126,6 +126,11 @@ struct itk_backend {
     int lane_stagger = 100;    // option decode_lane_stagger: how far lane 1 of a step's first launch starts behind lane 0,
                                // in per cent of the time lane 0 needs to stream its keys (0 = together)
     uint64_t res_lane0_tiles = 0;  // 64-key tiles of lane 0 in one launch when the loop began
+    // The uninterrupted run of tcgen05 multi-row launches at the end of the stream's queue: the layers they cover.
+    // A further launch on a layer outside it may stream its stored K/V before its predecessor completes (nothing that
+    // can still be running writes that layer's cache); any other queued work that writes the cache ends the run.
+    uint64_t tc_chain_mask = 0;
+    bool tc_chain_live = false;
     unsigned char* lane_hdr = nullptr;  // arrival counters of a single-GPU loop run in lanes (a gather header without data)
     uint32_t* d_plan = nullptr;  // the decode kernel's work plan of the loop's current positions (device words)
     itk::DecodePlanSpec res_spec{};
@@ -278,6 +283,7 @@ void fill_layer_view(const itk_backend* b, uint32_t layer, itk::LayerView* v) {
 // Launch the append kernel for `n` sequences (device sources).
 int run_append(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seqs, uint32_t rows, const float* d_k,
                const float* d_v) {
+    b->tc_chain_live = false;
     for (uint32_t at = 0; at < n; at += itk::kMaxSeqsPerLaunch) {
         const uint32_t m = (n - at < static_cast<uint32_t>(itk::kMaxSeqsPerLaunch)) ? n - at : itk::kMaxSeqsPerLaunch;
         AppendLaunch p{};
@@ -372,6 +378,7 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                                                  zu(b->ticket_cells));
         b->stats.kv_bytes_read += keys * b->cfg.kv_heads * D * 2ull * b->elem_bytes;
         const long ev = prof_begin(b, 0);
+        if (!verify_tc) b->tc_chain_live = false;
         if (decode) {
             if (d_k_new) {
                 p.k_new = d_k_new + static_cast<size_t>(at) * b->row_len();
@@ -398,7 +405,13 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                 p.v_new = d_v_new + static_cast<size_t>(at) * rows * b->row_len();
             }
             b->status_pending = true;
-            p.pdl = b->use_pdl ? 1u : 0u;
+            // behind an unbroken run of this kernel's launches on other layers, the K/V stream may start early
+            const bool early = b->use_pdl && b->tc_chain_live && layer < 64 && ((b->tc_chain_mask >> layer) & 1ull) == 0 &&
+                               b->prof_events.empty();
+            p.pdl = !b->use_pdl ? 0u : (early ? 2u : 1u);
+            if (!early) b->tc_chain_mask = 0;
+            b->tc_chain_live = layer < 64;
+            if (layer < 64) b->tc_chain_mask |= 1ull << layer;
 #ifdef ITK_DECODE_TRACE
             p.trace = g_trace;
 #endif
@@ -518,6 +531,7 @@ int ensure_gather(itk_backend* b, size_t bytes) {
 int run_copy(itk_backend* b, uint32_t slot, void* snap_base, const std::vector<uint32_t>& layers,
              const std::vector<uint64_t>& first, const std::vector<uint64_t>& rows, const std::vector<uint64_t>& k_off,
              const std::vector<uint64_t>& v_off, bool to_snapshot) {
+    b->tc_chain_live = false;
     const uint32_t row_bytes = b->cfg.head_dim * b->elem_bytes;
     const uint32_t vb = (row_bytes % 16 == 0) ? 16 : b->elem_bytes;
     const uint64_t units_per_row = static_cast<uint64_t>(b->cfg.kv_heads) * (row_bytes / vb);
@@ -1055,6 +1069,7 @@ static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q,
                                float* d_out, bool gather, uint64_t gather_offset_bytes) {
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
     if (int rc = check_layer(b, layer)) return rc;
+    b->tc_chain_live = false;
     AttnLaunch p{};
     bool two_lanes = false;
     fill_layer_view(b, layer, &p.layer);
@@ -1778,6 +1793,7 @@ int itk_reset(itk_backend* b, uint32_t slot) {
     if (!b) return ITK_ERR_INVALID_ARGUMENT;
     cudaSetDevice(b->cfg.device);
     if (int rc = check_slot(b, slot)) return rc;
+    b->tc_chain_live = false;
     // Ring layers read as zero-filled until written, like a fresh reference cache.
     for (uint32_t l = 0; l < b->cfg.n_layers; ++l)
         if (b->window[l] && b->slots[slot].appended[l] != 0) {

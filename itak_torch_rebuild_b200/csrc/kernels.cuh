@@ -109,6 +109,8 @@ struct AttnLaunch {
     uint32_t pdl;            // decode and tcgen05 multi-row kernels launched as a programmatic dependent of the previous kernel in the
                              // stream: 0 = no, 1 = wait for it before anything else, 2 = wait only after the first
                              // K/V tile loads are in flight (nothing the predecessor writes is read before the wait),
+                             // (tcgen05 multi-row kernel: its K/V loaders stream the layer's stored rows before the
+                             // wait; the backend grants it only behind launches of the same kernel on other layers),
                              // 3 = (decode kernel, two lanes) never wait for the predecessor before working - the
                              // lane's arrival counters order everything that is shared with it - and wait for it just
                              // before the CTA exits, so that grids still complete in stream order
