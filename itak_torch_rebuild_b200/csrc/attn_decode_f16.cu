@@ -457,8 +457,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m, mx);  // finite: key row0 is valid
-            const float corr = fast_exp2(m - m_new);
+            // The running maximum moves only when the slice's maximum exceeds it by more than 2^kRescaleStep: until
+            // then the stale one is used consistently for the weights (at most 2^kRescaleStep each), their sum and
+            // the accumulator, so the result is exact and the accumulator's rescale - 4 * NT multiplies per thread -
+            // is skipped for almost every tile after the first few.
+            constexpr float kRescaleStep = 8.f;
+            const bool grow = mx > m + kRescaleStep;  // also the first slice (m = -inf; mx is finite: key row0 is valid)
+            const float m_new = grow ? mx : m;
+            const bool rescale = __any_sync(0xffffffffu, grow);
+            const float corr = grow ? fast_exp2(m - m_new) : 1.f;
             m = m_new;
             uint32_t pa[4];
             float psum = 0.f;
@@ -473,12 +480,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 pa[2 * j + 1] = pack_half2(l0, l1);
             }
             l = l * corr + psum;
+            if (rescale) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                o[j][0] *= corr;
-                o[j][1] *= corr;
-                o[j][2] *= corr;
-                o[j][3] *= corr;
+                for (int j = 0; j < NT; ++j) {
+                    o[j][0] *= corr;
+                    o[j][1] *= corr;
+                    o[j][2] *= corr;
+                    o[j][3] *= corr;
+                }
             }
             // O(16 x D) += P(16 x 16 keys) * V(16 keys x D)
             {
