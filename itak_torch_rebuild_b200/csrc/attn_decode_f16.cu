@@ -267,6 +267,24 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         const __half* vb = static_cast<const __half*>(p.layer.v) + stream;
         const uint32_t kbuf = slice_addr(stage, 0), vbuf = slice_addr(stage, 1);
         const uint32_t row0 = c.tile * kTileKeys + warp * 16;
+        const uint32_t srow0 = c.s0 + row0 >= ring ? c.s0 + row0 - ring : c.s0 + row0;
+        if (row0 + 16 <= c.n - (fused ? 1u : 0u) && srow0 + 16 <= ring) {
+            // The whole slice is stored rows inside the ring (every slice but a sequence's last one or two and a
+            // sliding layer's wrap): this lane's copies differ by constants only.
+            const int r = lane / kChunksPerRow, ch = lane % kChunksPerRow;  // first of its rows, its 16-byte chunk
+            constexpr int kRowStep = 32 / kChunksPerRow;                    // rows between two copies of a lane
+            const size_t goff = static_cast<size_t>(srow0 + r) * D + ch * 8;
+            const __half* kg = kb + goff;
+            const __half* vg = vb + goff;
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) {
+                const int row = r + i * kRowStep;
+                const uint32_t soff = row * kRowBytes + ((ch ^ (row & 7)) << 4);
+                cp_async16(kbuf + soff, kg + static_cast<size_t>(i) * kRowStep * D, 16u);
+                cp_async16(vbuf + soff, vg + static_cast<size_t>(i) * kRowStep * D, 16u);
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < D / 16; ++i) {
             const int cid = i * 32 + lane;
