@@ -467,7 +467,7 @@ def measure_decode(args, env: Dist, workload, geom, steps, warmup, *, e2e=True, 
             block_ms.append(timed_block())
         clocks = sampler.stop() if sampler else None
         if fused:
-            gather_info = {"kind": "stores to peer memory from the decode kernel, arrival flags per source rank",
+            gather_info = {"kind": "stores to peer memory from the decode kernel, arrival counters per (sequence, source rank)",
                            "waits_timed_out": be.gather_status()}
         launches = steps * (layers + 1)  # per rank and block: one fused kernel per layer plus the position advance
 
