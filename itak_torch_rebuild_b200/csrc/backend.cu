@@ -209,7 +209,7 @@ int check_layer(const itk_backend* b, uint32_t layer) {
 // KV splits for a decode launch: minimise waves x (tiles per CTA + fixed cost)
 // over the CTA slots the device offers (2 resident CTAs per SM).
 uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uint32_t tile, uint64_t scratch_mult = 1,
-                       uint32_t ctas_per_sm = 2) {
+                       uint32_t ctas_per_sm = 2, uint32_t min_tiles = 4) {
     if (b->forced_splits > 0) {
         uint64_t s = static_cast<uint64_t>(b->forced_splits);
         const uint64_t by_len = (n_max + tile - 1) / tile;
@@ -219,7 +219,7 @@ uint32_t choose_splits(const itk_backend* b, uint64_t cells, uint64_t n_max, uin
         return static_cast<uint32_t>(s < 1 ? 1 : s);
     }
     const uint64_t slots = static_cast<uint64_t>(b->sm_count) * ctas_per_sm;
-    uint64_t max_s = (n_max + 4 * tile - 1) / (4 * tile);  // at least four tiles per CTA
+    uint64_t max_s = (n_max + min_tiles * tile - 1) / (min_tiles * tile);  // at least min_tiles tiles per CTA
     if (max_s < 1) max_s = 1;
     if (max_s > 256) max_s = 256;
     if (cells == 0) return 1;
@@ -332,6 +332,10 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                            itk::verify_tc_supported(D, rows, b->group);
     const bool verify = !verify_tc && b->f16 && !decode && !b->force_general &&
                         itk::verify_f16_supported(D, rows, b->group);
+    // (its query rows are read sixteen bytes at a time)
+    const bool f32_tc = !b->f16 && !b->force_general && itk::attn_f32_supported(D, rows) &&
+                        (reinterpret_cast<uintptr_t>(d_q) & 15u) == 0;
+    const uint32_t f32_pairs = f32_tc ? itk::attn_f32_pairs_per_cta(rows, b->group) : 0u;
     // grid.z carries n_seqs * rows (general kernel) and is limited to 65535
     uint32_t per_launch = itk::kMaxSeqsPerLaunch;
     while (per_launch > 1 && static_cast<uint64_t>(per_launch) * rows > 65535) per_launch >>= 1;
@@ -372,6 +376,7 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
         // times the scratch per (cell, split).
         const uint64_t cells = verify_tc ? static_cast<uint64_t>(m) * HY * itk::verify_tc_pair_chunks(rows, b->group)
                                : verify  ? static_cast<uint64_t>(m) * HY * itk::verify_pair_chunks(rows, b->group)
+                               : f32_tc  ? static_cast<uint64_t>(m) * HY * itk::attn_f32_pair_chunks(rows, b->group)
                                          : static_cast<uint64_t>(m) * rows * HY;
         if (cells > b->ticket_cells)
             return b->fail(ITK_ERR_CAPACITY, "attention: " + zu(cells) + " (row, head) cells exceed the scratch of " +
@@ -416,6 +421,30 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
             p.trace = g_trace;
 #endif
             ITK_CUDA(b, itk::launch_verify_tc(p, b->stream, &b->stats.kernel_launches), "tensor-core attention launch");
+            prof_end(b, ev);
+            continue;
+        }
+        if (f32_tc) {
+            // a slot of its scratch holds f32_pairs rows instead of 8; a decode block's CTAs may take a single 32-key
+            // tile each (the launch is latency-bound), a prefill block's at least four.  A block whose causal range
+            // is shorter than the longest one takes fewer parts (the kernel cuts every range into parts of one size).
+            // Under the causal bound a block of a long chunk walks, on average, the stored history plus half the
+            // chunk: the CTA count that fills the machine is estimated from that share of the cells.
+            uint64_t busy_cells = cells;
+            if (f32_pairs == 64 && n_max > 0) {
+                const uint64_t mean = n_max > rows / 2 ? n_max - rows / 2 : 1;
+                busy_cells = (cells * mean + n_max - 1) / n_max;
+                if (busy_cells < 1) busy_cells = 1;
+            }
+            p.splits = choose_splits(b, busy_cells, n_max, 32, 0, D == 64 ? 4 : 2, f32_pairs == 16 ? 1 : 4);
+            while (p.splits > 1 && static_cast<uint64_t>(p.splits) * cells * (f32_pairs / 8) > kPartCellSplits) --p.splits;
+            if (p.splits > itk::attn_f32_max_parts()) p.splits = itk::attn_f32_max_parts();
+            b->stats.last_splits = p.splits;
+            if (d_k_new) {
+                p.k_new = d_k_new + static_cast<size_t>(at) * rows * b->row_len();
+                p.v_new = d_v_new + static_cast<size_t>(at) * rows * b->row_len();
+            }
+            ITK_CUDA(b, itk::launch_attn_f32(p, b->stream, &b->stats.kernel_launches), "f32 attention launch");
             prof_end(b, ev);
             continue;
         }
@@ -495,11 +524,17 @@ int validate_step(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_
     return ITK_OK;
 }
 
+// And the tensor-core kernel of an f32 cache, for any number of rows (the append is a plain copy there).
+bool f32_fuses_append(const itk_backend* b, uint32_t rows) {
+    return !b->f16 && !b->separate_append && !b->force_general && itk::attn_f32_supported(b->cfg.head_dim, rows);
+}
+
 int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots, const uint64_t* positions,
                 uint32_t rows, const float* d_q, const float* d_k, const float* d_v, float* d_out) {
     std::vector<SeqDesc> seqs;
     if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
-    const bool fuse = decode_fuses_append(b, rows) || verify_fuses_append(b, rows);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) & 15u) == 0;
+    const bool fuse = decode_fuses_append(b, rows) || verify_fuses_append(b, rows) || (aligned && f32_fuses_append(b, rows));
     if (!fuse)
         if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
     // The positions move only once the launch that stores the rows (the fused kernels) has been queued: a refused
@@ -653,6 +688,7 @@ int itk_backend_create(const itk_config* cfg, itk_backend** out) {
     e = itk::configure_decode_f16();
     if (e == cudaSuccess) e = itk::configure_verify_f16();
     if (e == cudaSuccess) e = itk::configure_verify_tc();
+    if (e == cudaSuccess) e = itk::configure_attn_f32();
     if (e != cudaSuccess) return cuda_refuse(e, "kernel attribute setup");
     e = cudaStreamCreateWithFlags(&b->own_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) return cuda_refuse(e, "cudaStreamCreate");

@@ -315,6 +315,15 @@ bool verify_tc_supported(uint32_t head_dim, uint32_t rows, uint32_t group);
 uint32_t verify_tc_pairs_per_cta(uint32_t rows, uint32_t group);
 uint32_t verify_tc_pair_chunks(uint32_t rows, uint32_t group);
 cudaError_t configure_verify_tc();
+// Attention over an f32 cache on the tensor cores (three-term tf32 products), head_dim 64 or 128, any number of rows.
+// With AttnLaunch::k_new / v_new set it stores the call's new rows itself (no append launch).
+// A cell of its scratch is a (sequence, head chunk, block of attn_f32_pairs_per_cta row-head pairs).
+cudaError_t launch_attn_f32(const AttnLaunch& p, cudaStream_t s, uint64_t* launches);
+bool attn_f32_supported(uint32_t head_dim, uint32_t rows);
+uint32_t attn_f32_pairs_per_cta(uint32_t rows, uint32_t group);
+uint32_t attn_f32_pair_chunks(uint32_t rows, uint32_t group);
+uint32_t attn_f32_max_parts();  // most parts one block's key range is cut into
+cudaError_t configure_attn_f32();
 // General kernel: any head_dim <= 256, any rows, f32 or f16 cache (CUDA cores, f32 math).
 cudaError_t launch_attn_general(const AttnLaunch& p, bool f16, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_snapshot_copy(const CopyLaunch& p, cudaStream_t s, uint64_t* launches);
