@@ -141,8 +141,9 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * (crates/itak-kv/src/config.rs).  Names: "decode_ctas" (persistent CTAs of the decode kernel, 0 = two per SM),
  * "decode_splits" (KV splits of the general and multi-row kernels, 0 = chosen per launch), "pdl" (programmatic
  * dependent launch inside the replayable loop, default 1), "decode_fused_sum" (cells shared by many CTAs are summed
- * in L2, default 1), "separate_append" (decode steps launch the append kernel separately, default 0),
- * "force_general" (multi-row calls take the CUDA-core kernel, default 0), "verify_tc" (multi-row calls take the
+ * in L2, default 1), "separate_append" (the append kernel runs as a launch of its own instead of the attention
+ * kernel storing the call's new rows, default 0), "force_general" (multi-row calls on an f16 cache and every call
+ * on an f32 cache take the CUDA-core kernel, default 0), "verify_tc" (multi-row calls take the
  * tcgen05 kernel, default 1), "gather_poll_limit" (polls of a peer's arrival flag before the fused gather's wait
  * gives up, default 200000), "decode_lanes" (two-lane schedule of the gathering loop: 0 never, 1 when a launch is
  * short enough to gain, 2 whenever possible; default 1), "decode_lane_stagger" (how far the second lane of a step's
