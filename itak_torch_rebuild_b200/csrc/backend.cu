@@ -332,9 +332,7 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                            itk::verify_tc_supported(D, rows, b->group);
     const bool verify = !verify_tc && b->f16 && !decode && !b->force_general &&
                         itk::verify_f16_supported(D, rows, b->group);
-    // (its query rows are read sixteen bytes at a time)
-    const bool f32_tc = !b->f16 && !b->force_general && itk::attn_f32_supported(D, rows) &&
-                        (reinterpret_cast<uintptr_t>(d_q) & 15u) == 0;
+    const bool f32_tc = !b->f16 && !b->force_general && itk::attn_f32_supported(D, rows);
     const uint32_t f32_pairs = f32_tc ? itk::attn_f32_pairs_per_cta(rows, b->group) : 0u;
     // grid.z carries n_seqs * rows (general kernel) and is limited to 65535
     uint32_t per_launch = itk::kMaxSeqsPerLaunch;
@@ -524,6 +522,16 @@ int validate_step(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_
     return ITK_OK;
 }
 
+// The device buffers of a call must start on 16-byte boundaries (the kernels move them as 16-byte vectors):
+// a named refusal instead of a misaligned-address fault.
+template <typename... P>
+int check_device_alignment(itk_backend* b, const char* what, P... ptrs) {
+    const uintptr_t all = (... | reinterpret_cast<uintptr_t>(ptrs));
+    if ((all & 15u) != 0)
+        return b->fail(ITK_ERR_INVALID_ARGUMENT, std::string(what) + ": device buffers must be 16-byte aligned");
+    return ITK_OK;
+}
+
 // And the tensor-core kernel of an f32 cache, for any number of rows (the append is a plain copy there).
 bool f32_fuses_append(const itk_backend* b, uint32_t rows) {
     return !b->f16 && !b->separate_append && !b->force_general && itk::attn_f32_supported(b->cfg.head_dim, rows);
@@ -533,8 +541,7 @@ int step_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t*
                 uint32_t rows, const float* d_q, const float* d_k, const float* d_v, float* d_out) {
     std::vector<SeqDesc> seqs;
     if (int rc = validate_step(b, layer, n_seqs, slots, positions, rows, &seqs)) return rc;
-    const bool aligned = ((reinterpret_cast<uintptr_t>(d_q) | reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) & 15u) == 0;
-    const bool fuse = decode_fuses_append(b, rows) || verify_fuses_append(b, rows) || (aligned && f32_fuses_append(b, rows));
+    const bool fuse = decode_fuses_append(b, rows) || verify_fuses_append(b, rows) || f32_fuses_append(b, rows);
     if (!fuse)
         if (int rc = run_append(b, layer, n_seqs, seqs.data(), rows, d_k, d_v)) return rc;
     // The positions move only once the launch that stores the rows (the fused kernels) has been queued: a refused
@@ -1104,6 +1111,7 @@ extern "C" int itk_debug_trace_buffer(void** dev_ptr, uint64_t* bytes) {
 static int resident_layer_impl(itk_backend* b, uint32_t layer, const float* d_q, const float* d_k, const float* d_v,
                                float* d_out, bool gather, uint64_t gather_offset_bytes) {
     if (!b->res_active) return b->fail(ITK_ERR_INVALID_ARGUMENT, "resident loop: not active");
+    if (int rc = check_device_alignment(b, "resident loop", d_q, d_k, d_v, d_out)) return rc;  // (a null d_out is aligned)
     if (int rc = check_layer(b, layer)) return rc;
     b->tc_chain_live = false;
     AttnLaunch p{};
@@ -1366,6 +1374,7 @@ int itk_attention_batch_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, 
                                const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
                                const float* d_v, float* d_out) {
     if (!b || !slots || !positions || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_device_alignment(b, "attention", d_q, d_k, d_v, d_out)) return rc;
     cudaSetDevice(b->cfg.device);
     return step_device(b, layer, n_seqs, slots, positions, rows, d_q, d_k, d_v, d_out);
 }
@@ -1561,6 +1570,7 @@ int itk_attention_batch_prep_device(itk_backend* b, uint32_t layer, uint32_t n_s
                                     const uint64_t* positions, uint32_t rows, const float* d_q, const float* d_k,
                                     const float* d_v, float* d_out) {
     if (!b || !slots || !positions || !d_q || !d_k || !d_v || !d_out) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_device_alignment(b, "attention", d_q, d_k, d_v, d_out)) return rc;
     cudaSetDevice(b->cfg.device);
     return step_prepared(b, layer, n_seqs, slots, positions, rows, d_q, d_k, d_v, d_out);
 }
@@ -1694,6 +1704,7 @@ int itk_append_rows(itk_backend* b, uint32_t slot, uint32_t layer, const float* 
 int itk_append_rows_device(itk_backend* b, uint32_t layer, uint32_t n_seqs, const uint32_t* slots,
                            const uint64_t* starts, uint32_t rows, const float* d_k, const float* d_v) {
     if (!b || !slots || !starts || !d_k || !d_v) return ITK_ERR_INVALID_ARGUMENT;
+    if (int rc = check_device_alignment(b, "append", d_k, d_v)) return rc;
     cudaSetDevice(b->cfg.device);
     if (int rc = check_layer(b, layer)) return rc;
     if (n_seqs == 0 || rows == 0) return ITK_OK;

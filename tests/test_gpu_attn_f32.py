@@ -215,3 +215,33 @@ def test_ragged_batch_of_slots():
             at[i] += rows
     assert TIGHT < TOL_F32_KV
     gpu.close()
+
+
+def test_unaligned_device_buffers_are_refused_by_name():
+    """Device buffers must start on 16-byte boundaries (the kernels move them as 16-byte vectors): a buffer that does
+    not is a named refusal that launches nothing and leaves the slot where it was."""
+    import ctypes as C
+
+    import torch
+
+    from itak_torch_rebuild_b200.backend import CudaComputeError
+
+    hq, hkv, d, n0 = 8, 2, 64, 100
+    gpu, refs = build([0], hq, hkv, d, n0, 1, seed=21)
+    dev = torch.device("cuda", 0)
+    tq = torch.zeros(hq * d + 4, device=dev)
+    tk = torch.zeros(hkv * d + 4, device=dev)
+    tv = torch.zeros(hkv * d + 4, device=dev)
+    out = torch.empty(hq * d, device=dev)
+    before = gpu.stats()["kernel_launches"]
+    one, at = (C.c_uint32 * 1)(0), (C.c_uint64 * 1)(n0)
+    for off_q, off_k in ((4, 0), (0, 4), (8, 8)):
+        with pytest.raises(CudaComputeError, match="16-byte aligned"):
+            gpu.attention_batch_ptrs(0, one, at, 1, 1, tq.data_ptr() + off_q, tk.data_ptr() + off_k, tv.data_ptr(),
+                                     out.data_ptr(), device=True)
+    assert gpu.stats()["kernel_launches"] == before
+    gpu.attention_batch_ptrs(0, one, at, 1, 1, tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), device=True)
+    gpu.synchronize()
+    refs[0].append(0, np.zeros(hkv * d, np.float32), np.zeros(hkv * d, np.float32), n0)
+    assert_view_equal(gpu, refs[0], 0, DTYPE)
+    gpu.close()
