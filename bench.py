@@ -13,7 +13,8 @@ Prints ONE JSON line: decode steps/s (whole job), with
   clocks        - SM clocks and throttle reasons sampled during the timed region,
   gather_check  - N > 1: the fused gather's buffer compared with an NCCL all-gather of the same step, every rank,
   paths         - N = 1: short measurements of the other configurations (single-sequence decode, continuous
-                  batching, the f32 prefill + decode case, prefix restore, speculative verify), see bench_paths.py.
+                  batching, the f32 prefill + decode case, prefix restore, speculative verify, chunked prefill), see
+                  bench_paths.py.
 The `--steps` block is replayed several times (the same positions each time) until about a second has been
 timed; `value` is the median block, min / max and the block count are in `blocks`.
 `--impl reference` times only the CPU restatement (the reference's own CPU path cannot be built here: it is Rust).
@@ -40,7 +41,7 @@ WORKLOADS = {
     "c5_long_context_decode": (48, 64, 8, 128, 8, 32768),
     "c2_single_sequence_decode": (32, 32, 8, 128, 1, 4096),
 }
-PATH_WORKLOADS = ["c1_tinyllama_f32", "c3_continuous_batching", "c4_prefix_restore", "c4_spec_verify"]
+PATH_WORKLOADS = ["c1_tinyllama_f32", "c3_continuous_batching", "c4_prefix_restore", "c4_spec_verify", "c4_chunked_prefill"]
 METRIC = "decode_attention_steps_per_s"
 UNIT = "steps/s"
 # DRAM traffic of one decode launch relative to its algorithmic KV bytes, from an ncu capture of this kernel at

@@ -14,6 +14,11 @@ length with `--workload NAME`):
                           7 rows + causal verify attention over them on every layer, then truncate to 1 + accepted
                           rows (accepted ~ geometric(0.7) capped at 6).  Roofline: HBM, the K/V the block sees.
 
+  c4_chunked_prefill      that model's prompt ingestion: 4 sessions x 2048 tokens, every layer fed in chunks of 512 rows
+                          (one multi-row call per layer and chunk: the chunk's rows are appended and attended
+                          causally).  Metric: prompt tokens/s.  Roofline: the tensor pipe (useful flops = 4 x rows x
+                          heads x visible keys x head dim against the measured dense bf16 rate).
+
 Every line carries `roofline` (the dominant kernel's algorithmic bytes over its CUDA-event time against the measured
 HBM peak), `e2e` (the same work driven from host buffers through the C ABI) and `cpu_baseline` (the CPU restatement
 of the reference on the same shape, a bounded sample).  Inputs are seeded synthetic N(0,1) tensors.
@@ -355,6 +360,135 @@ def run_spec_verify(args, sampler_cls, short=False):
 
 
 # ---------------------------------------------------------------------------------------------------------
+# config 4's model, prompt ingestion: chunked prefill on the multi-row tensor-core kernel
+# ---------------------------------------------------------------------------------------------------------
+def run_chunked_prefill(args, sampler_cls, short=False):
+    import numpy as np
+
+    from itak_torch_rebuild_b200 import CudaCompute, KvDtype
+    from oracle import oracle as orc
+
+    layers = getattr(args, "layers", None) or LAYERS
+    sessions, prompt, chunk = 4, PREFIX, 512
+    chunks = prompt // chunk
+    warm = max(args.warmup, 3)
+    reps = 3 if short else max(args.steps, 5)
+    torch, dev, stream, gen = _device()
+    be = CudaCompute(layers, HQ, HKV, D, n_slots=sessions, max_context=prompt + 8, chunk_cap=chunk, kv_dtype=KvDtype.F16,
+                     device=0, options=_options(args))
+    be.set_stream(stream.cuda_stream)
+    gen.manual_seed(17)
+    # one chunk's rows per layer, reused for every chunk (the values do not change the work)
+    q = torch.randn((layers, sessions, chunk, HQ * D), device=dev, generator=gen)
+    k = torch.randn((layers, sessions, chunk, HKV * D), device=dev, generator=gen)
+    v = torch.randn((layers, sessions, chunk, HKV * D), device=dev, generator=gen)
+    out = torch.empty((layers, sessions, chunk, HQ * D), device=dev)
+    slots_c = (C.c_uint32 * sessions)(*range(sessions))
+
+    def ingest(profile=False, n_chunks=chunks):
+        """All sessions' prompts, chunk by chunk through every layer; returns (ms, profile)."""
+        for s in range(sessions):
+            be.reset(s)
+        if profile:
+            be.profile_enable(chunks * layers * 2 + 8)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for c in range(n_chunks):
+            pc = (C.c_uint64 * sessions)(*([c * chunk] * sessions))
+            for layer in range(layers):
+                be.attention_batch_ptrs(layer, slots_c, pc, sessions, chunk, q[layer].data_ptr(), k[layer].data_ptr(),
+                                        v[layer].data_ptr(), out[layer].data_ptr(), device=True)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        prof = None
+        if profile:
+            prof = be.profile_read()
+            be.profile_enable(0)
+        return e0.elapsed_time(e1), prof
+
+    for _ in range(warm):
+        ingest()
+    launches0 = be.stats()["kernel_launches"]
+    sampler = sampler_cls(0)
+    sampler.start()
+    times = sorted(ingest()[0] for _ in range(reps))
+    clocks = sampler.stop()
+    launches = be.stats()["kernel_launches"] - launches0
+    ms = times[len(times) // 2]
+    _, prof = ingest(profile=True)
+    be.synchronize()  # raises if a bounded wait of the tensor-core kernel ran out
+
+    # end to end from pinned host buffers: the last chunk of every session, all layers in one call
+    hq_pin = q.cpu().pin_memory()
+    hk_pin, hv_pin = k.cpu().pin_memory(), v.cpu().pin_memory()
+    ho_pin = torch.empty_like(hq_pin).pin_memory()
+
+    def host_chunk():
+        cps = [be.cache_checkpoint(chunk, slot=s) for s in range(sessions)]
+        pc = (C.c_uint64 * sessions)(*([prompt - chunk] * sessions))
+        t0 = time.perf_counter()
+        be.attention_layers_host_ptrs(slots_c, pc, sessions, chunk, hq_pin.data_ptr(), hk_pin.data_ptr(), hv_pin.data_ptr(),
+                                      ho_pin.data_ptr())
+        dt = time.perf_counter() - t0
+        for s in range(sessions):  # back to the state before the chunk (host metadata only)
+            be.cache_rewind(cps[s], prompt - chunk, slot=s)
+            be.cache_release(cps[s], slot=s)
+        return dt
+
+    ingest(n_chunks=chunks - 1)
+    host_chunk()
+    e2e_s = sorted(host_chunk() for _ in range(3))[1]
+    e2e = {"value": sessions * chunk / e2e_s, "unit": "tokens/s",
+           "h2d_bytes_per_step": layers * sessions * chunk * (HQ + 2 * HKV) * D * 4,
+           "d2h_bytes_per_step": layers * sessions * chunk * HQ * D * 4, "steps": 3,
+           "call": "itk_attention_layers_host on the prompt's last 512-row chunk of every session (pinned host "
+                   "q/k/v/out of all layers, uploads / kernels / downloads of consecutive layers overlapped)"}
+
+    # CPU: the reference's gqa_attention on sampled rows of one (session, layer) prefill, all cores
+    threads = os.cpu_count() or 1
+    rows_sample = [int(x) for x in np.linspace(0, prompt - 1, threads)]
+    qh = np.random.default_rng(9).standard_normal((threads, HQ * D), dtype=np.float32)
+    views = [_oracle_cache(HKV, D, r + 1, seed=r).view(0) for r in rows_sample]  # row r attends its causal prefix
+    secs = _threads_run(lambda i: orc.gqa_attention(qh[i], 1, HQ, [rows_sample[i]], views[i]), range(threads), threads)
+    # rows sampled evenly over the causal triangle: their mean cost is the mean row's
+    cpu_s = secs / threads * prompt * sessions * layers
+    cpu = {"value": sessions * prompt / cpu_s, "unit": "tokens/s", "cores": threads, "kind": "port",
+           "sample": f"{threads} rows spread evenly over one (session, layer) prompt of {prompt} tokens (each attends its "
+                     f"causal prefix in an f32 cache), {threads} host threads, extrapolated to {sessions} sessions x {layers} layers"}
+
+    tpeak, tsrc = _tensor_peak()
+    peak, _ = _peak()
+    flops = 4.0 * HQ * D * (prompt * (prompt + 1) / 2) * sessions * layers
+    n_launch = chunks * layers
+    a_ms = prof["attention_ms"] / max(prof["attention_launches"], 1)
+    kv_bytes = sum((c + 1) * chunk for c in range(chunks)) * sessions * HKV * D * 2 * 2 * layers
+    verify_tc = bool(_options(args).get("verify_tc", 1))
+    line = {
+        "metric": "prefill_tokens_per_s", "value": sessions * prompt * 1e3 / ms, "unit": "tokens/s", "n_gpus": 1,
+        "steps": reps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 math over an f16 KV cache (queries and weights as two f16 terms)", "data": "synthetic",
+        "config": {"workload": "c4_chunked_prefill", "layers": layers, "q_heads": HQ, "kv_heads": HKV, "head_dim": D,
+                   "sessions": sessions, "prompt_tokens": prompt, "chunk_rows": chunk,
+                   "launch": "one multi-row call per layer and chunk: the append kernel stores the chunk's rows, then the "
+                             "attention kernel attends them causally (two launches; a block of up to 64 rows is stored by "
+                             "the attention kernel itself)",
+                   "l2": f"{kv_bytes / n_launch / 2**20:.0f} MiB of K/V per launch on average: L2-resident, the launch is "
+                         "bound by the tensor pipe, not by HBM"},
+        "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": tpeak, "unit": "TFLOP/s",
+                     "frac": flops / (ms * 1e-3) / 1e12 / tpeak, "traffic": None, "peak_source": tsrc,
+                     "kernel": "verify_tc_kernel (tcgen05)" if verify_tc else "verify_f16_kernel<128> (mma.sync)",
+                     "flops_per_launch": flops / n_launch, "avg_launch_ms": ms / n_launch, "launches_timed": reps * n_launch,
+                     "useful_flops": "4 x rows x heads x visible keys x head dim; the kernel executes twice that on a full "
+                                     "block (every query row and weight row as a hi and a lo f16 term)",
+                     "event_pair": {"avg_launch_ms": a_ms, "launches_timed": prof["attention_launches"]},
+                     "kv_read_gbs": kv_bytes / (ms * 1e-3) / 1e9, "kv_read_frac_of_hbm_peak": kv_bytes / (ms * 1e-3) / 1e9 / peak},
+        "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks, "gpu_launches": launches,
+    }
+    be.close()
+    return line
+
+
+# ---------------------------------------------------------------------------------------------------------
 # config 3: continuous batching over ragged slots with retire / refill
 # ---------------------------------------------------------------------------------------------------------
 def run_continuous_batching(args, sampler_cls, short=False):
@@ -660,4 +794,5 @@ RUNNERS = {
     "c3_continuous_batching": run_continuous_batching,
     "c4_prefix_restore": run_prefix_restore,
     "c4_spec_verify": run_spec_verify,
+    "c4_chunked_prefill": run_chunked_prefill,
 }

@@ -168,7 +168,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     const uint32_t split = blockIdx.x, seq = blockIdx.z;
     const uint32_t gheads = min(p.group, static_cast<uint32_t>(kHeadsPerCta));
     const uint32_t pchunks = (p.rows * gheads + PC - 1) / PC;
-    const uint32_t hy = blockIdx.y / pchunks, pc = blockIdx.y % pchunks;
+    // pair blocks are handed out last block first: under the causal bound it has the longest key range, and the
+    // CTAs placed in the launch's last wave should be the short ones
+    const uint32_t hy = blockIdx.y / pchunks, pc = pchunks - 1 - blockIdx.y % pchunks;
     const SeqDesc sd = p.seq[seq];
     const uint32_t kvh = hy / p.gchunks, gc = hy % p.gchunks;
     const uint32_t head0 = kvh * p.group + gc * kHeadsPerCta;

@@ -464,9 +464,13 @@ bool decode_fuses_append(const itk_backend* b, uint32_t rows) {
     return b->f16 && !b->separate_append && (b->cfg.head_dim % 8 == 0) && itk::decode_f16_supported(b->cfg.head_dim, rows);
 }
 
-// So does the tcgen05 multi-row kernel (its loader warps convert and store the block's rows).
+// So does the tcgen05 multi-row kernel for a short block (its loader warps convert the block's rows on their way
+// into the staged tiles and store them).  A long chunk's rows are most of what its tiles hold, and converting them
+// in the two loader warps of every CTA that reads them costs far more than the append kernel's launch: from
+// kVerifyFuseMaxRows rows on, the rows are appended first and every tile comes from the cache.
+constexpr uint32_t kVerifyFuseMaxRows = 64;
 bool verify_fuses_append(const itk_backend* b, uint32_t rows) {
-    return b->f16 && !b->separate_append && !b->force_general && b->verify_tc && rows > 1 &&
+    return b->f16 && !b->separate_append && !b->force_general && b->verify_tc && rows > 1 && rows <= kVerifyFuseMaxRows &&
            itk::verify_tc_supported(b->cfg.head_dim, rows, b->group);
 }
 
