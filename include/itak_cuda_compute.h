@@ -147,7 +147,11 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * tcgen05 kernel, default 1), "gather_poll_limit" (polls of a peer's arrival flag before the fused gather's wait
  * gives up, default 200000), "decode_lanes" (two-lane schedule of the gathering loop: 0 never, 1 when a launch is
  * short enough to gain, 2 whenever possible; default 1), "decode_lane_stagger" (how far the second lane of a step's
- * first launch starts behind the first, in per cent of the time the first needs to stream its keys; default 100).  Unknown names and out-of-range values are refused; not allowed inside
+ * first launch starts behind the first, in per cent of the time the first needs to stream its keys; default 100),
+ * "layers_host_bulk_bytes" (itk_attention_layers_host: a forward that uploads no more than this many bytes sends
+ * all layers' rows up in three copies, launches the layers back to back and brings the results down in one copy,
+ * instead of pipelining per-layer copies against the kernels; default 4 MiB, 0 = always pipeline).
+ * Unknown names and out-of-range values are refused; not allowed inside
  * a resident loop. */
 int itk_set_option(itk_backend* b, const char* name, int64_t value);
 int itk_synchronize(itk_backend* b);
@@ -188,7 +192,9 @@ int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const u
  * on the host (a benchmark of the path alone, a replay of recorded activations): host q [layers][n_seqs][rows][q_heads*D],
  * k, v [layers][n_seqs][rows][kv_heads*D], out like q; every slot must sit at positions[i] on every layer.  The
  * backend pipelines the layers over three streams - layer l's rows upload while layer l-1 computes and layer l-2's
- * result downloads - and returns after the last result is in `out`.  Same refusals as itk_attention_batch, all
+ * result downloads - and returns after the last result is in `out`; a small forward (see the option
+ * "layers_host_bulk_bytes") instead sends every layer's rows up in three strided copies, launches the layers back to
+ * back and brings all results down in one copy, since per-layer copies would cost more than their overlap hides.  Same refusals as itk_attention_batch, all
  * layers validated before anything is queued.  The first call allocates the per-layer staging.  No counterpart in
  * the reference, whose forward calls Compute::attention layer by layer (crates/muse-glimmer/src/model.rs:452-462). */
 int itk_attention_layers_host(itk_backend* b, uint32_t n_seqs, const uint32_t* slots, const uint64_t* positions,

@@ -107,6 +107,7 @@ struct itk_backend {
     int sm_count = 148;
     int forced_splits = 0;
     int forced_ctas = 0;         // option decode_ctas: persistent CTAs of the decode kernel (default 2 per SM)
+    uint64_t fw_bulk_bytes = 4ull << 20;  // option layers_host_bulk_bytes: forwards that upload no more take the bulk path
     bool separate_append = false;  // option separate_append = 1: decode steps launch the append kernel separately
     bool force_general = false;  // option force_general = 1: multi-row launches take the CUDA-core kernel (A/B checks)
     bool verify_tc = true;       // option verify_tc = 0: multi-row launches take the mma.sync kernel instead of tcgen05
@@ -851,6 +852,11 @@ int itk_set_option(itk_backend* b, const char* name, int64_t value) {
         b->gth_poll_limit = static_cast<uint32_t>(value);
         return ITK_OK;
     }
+    if (key == "layers_host_bulk_bytes") {
+        if (value < 0 || value > (1ll << 40)) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: layers_host_bulk_bytes must be 0..2^40");
+        b->fw_bulk_bytes = static_cast<uint64_t>(value);
+        return ITK_OK;
+    }
     return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: unknown option '" + key + "'");
 }
 
@@ -1445,6 +1451,24 @@ int itk_attention_layers_host(itk_backend* b, uint32_t n_seqs, const uint32_t* s
     }
     const size_t qn = total_rows * b->q_width(), kn = total_rows * b->row_len();
     const size_t qs = b->fw_rows * b->q_width(), ks = b->fw_rows * b->row_len();  // per-layer staging strides
+    if (static_cast<uint64_t>(L) * (qn + 2 * kn) * sizeof(float) <= b->fw_bulk_bytes) {
+        // A small forward (a decode step of a few sequences): the per-layer copies' fixed cost would outweigh what
+        // their overlap with the kernels hides.  Every layer's rows go up in three strided copies, the layers'
+        // launches follow back to back, one strided copy brings all results down.
+        const size_t f = sizeof(float);
+        ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_q, qs * f, q, qn * f, qn * f, L, cudaMemcpyHostToDevice, b->stream), "q upload");
+        ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_k, ks * f, k, kn * f, kn * f, L, cudaMemcpyHostToDevice, b->stream), "k upload");
+        ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_v, ks * f, v, kn * f, kn * f, L, cudaMemcpyHostToDevice, b->stream), "v upload");
+        for (uint32_t l = 0; l < L; ++l)
+            if (int rc = step_device(b, l, n_seqs, slots, positions, rows, b->fw_q + l * qs, b->fw_k + l * ks,
+                                     b->fw_v + l * ks, b->fw_out + l * qs))
+                return rc;
+        ITK_CUDA(b, cudaMemcpy2DAsync(out, qn * f, b->fw_out, qs * f, qn * f, L, cudaMemcpyDeviceToHost, b->stream),
+                 "output download");
+        queue_status_read(b);
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "forward");
+        return check_status(b);
+    }
     // The uploads start once everything already queued on the backend's stream (an earlier forward's kernels,
     // which read the same staging) has run.
     ITK_CUDA(b, cudaEventRecord(b->fw_ev_prev, b->stream), "forward");

@@ -13,12 +13,16 @@ from oracle import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("bulk", [True, False], ids=["bulk-copies", "pipelined-copies"])
 @pytest.mark.parametrize("dtype,d,rows", [(KvDtype.F16, 128, 1), (KvDtype.F16, 128, 7), (KvDtype.F32, 64, 1), (KvDtype.F32, 64, 5)])
-def test_one_call_per_forward_equals_one_call_per_layer(dtype, d, rows):
+def test_one_call_per_forward_equals_one_call_per_layer(dtype, d, rows, bulk):
+    """Both forms of the call: a small forward's bulk copies (the default at this size) and, with the threshold at
+    zero, the per-layer copies pipelined against the kernels."""
     layer_window, hq, hkv = [0, 0, 24, 0], 8, 2
     lens = [130, 33, 77]
     layers, n = len(layer_window), len(lens)
-    a, refs = make_pair(layer_window, hq, hkv, d, dtype=dtype, n_slots=n, max_context=256, chunk_cap=8)
+    a, refs = make_pair(layer_window, hq, hkv, d, dtype=dtype, n_slots=n, max_context=256, chunk_cap=8,
+                        options=None if bulk else {"layers_host_bulk_bytes": 0})
     b, _ = make_pair(layer_window, hq, hkv, d, dtype=dtype, n_slots=n, max_context=256, chunk_cap=8)
     rng = np.random.default_rng(d + rows)
     for slot, ln in enumerate(lens):
