@@ -21,10 +21,11 @@
 //   WK = 4  decode (at most 16 pairs): all four warps own the same 16 pairs
 //           and each walks a quarter of the tile's keys; their results are
 //           merged through shared memory at the end.
-// K/V tiles are staged once per CTA by cp.async into XOR-swizzled shared
-// memory (bank-conflict-free for both operand patterns) and split into hi/lo
-// terms as the fragments are read.  Small tiles and two stages keep a CTA at
-// 48 KiB (head_dim 64) so that four CTAs - sixteen warps - share an SM: the
+// K/V tiles are staged once per CTA by cp.async into shared memory with a
+// row pitch of D + 4 floats (bank-conflict-free for both operand patterns,
+// every fragment address a constant away from the thread's base) and split
+// into hi/lo terms as the fragments are read.  Small tiles and two stages keep a CTA at
+// 51 KiB (head_dim 64) so that four CTAs - sixteen warps - share an SM: the
 // warps' chains of conversions and dependent products hide behind each other.
 // The key range of a pair block ends at the block's last row (causal bound)
 // and starts at its first row's window.  It is cut into parts of one size per
@@ -85,11 +86,15 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
     constexpr int PC = 16 * PB;                // pairs per CTA
     constexpr int KW = kF32Tile / WK;          // keys of a tile one warp walks
     constexpr int kChunks = D / 4;             // 16-byte chunks per row
-    constexpr int kTileFloats = kF32Tile * D;  // one K (or V) tile
+    constexpr int LD = D + 4;                   // row pitch in shared memory, floats (see below)
+    constexpr int kTileFloats = kF32Tile * LD;  // one K (or V) tile
     constexpr int KS = D / 8, NT = D / 8;
 
-    float* q_s = reinterpret_cast<float*>(smem);  // [PC][D], chunk c of row r at c ^ (r & 7)
-    float* tiles = q_s + PC * D;                  // kStages x (K tile, V tile); the warps' results afterwards
+    // Rows of D floats sit LD = D + 4 floats apart: with a pitch of 4 (mod 32) banks the eight rows x four columns
+    // of a K (or Q) fragment read and the four rows x eight columns of a V fragment read both touch 32 different
+    // banks, and every fragment address is the thread's base plus a compile-time constant.
+    float* q_s = reinterpret_cast<float*>(smem);  // [PC][LD]
+    float* tiles = q_s + PC * LD;                 // kStages x (K tile, V tile); the warps' results afterwards
     __shared__ float res_m[4][16], res_l[4][16];
     __shared__ int s_flag;
 
@@ -174,8 +179,8 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
                 ksrc = knew + noff;
                 vsrc = vnew + noff;
             }
-            cp_async16(kbuf + row * (D * 4) + ((c ^ (row & 7)) << 4), ksrc, valid ? 16u : 0u);
-            cp_async16(vbuf + row * (D * 4) + ((c ^ (row & 6)) << 4), vsrc, valid ? 16u : 0u);
+            cp_async16(kbuf + row * (LD * 4) + (c << 4), ksrc, valid ? 16u : 0u);
+            cp_async16(vbuf + row * (LD * 4) + (c << 4), vsrc, valid ? 16u : 0u);
         }
     };
 #pragma unroll
@@ -184,7 +189,7 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
         cp_async_commit();
     }
 
-    // The block's query rows, swizzled like a K tile (dead pairs read as zero).
+    // The block's query rows, pitched like a K tile (dead pairs read as zero).
     for (uint32_t i = tid; i < PC * kChunks; i += kF32Threads) {
         const uint32_t q = i / kChunks, c = i % kChunks;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -193,7 +198,7 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
             const uint32_t r = gp / nh, h = gp % nh;
             v = __ldg(reinterpret_cast<const float4*>(p.q + ((static_cast<size_t>(seq) * p.rows + r) * p.q_heads + head0 + h) * D) + c);
         }
-        *reinterpret_cast<float4*>(q_s + q * D + ((c ^ (q & 7)) << 2)) = v;
+        *reinterpret_cast<float4*>(q_s + q * LD + (c << 2)) = v;
     }
 
     // This thread's two pairs: rows g and g + 8 of the warp's m16 tile.
@@ -215,8 +220,8 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const float sl = p.scale * kLog2e;
-    const float* qrow0 = q_s + (pb * 16 + g) * D;  // (g + 8) & 7 == g: both rows share the swizzle term
-    const float* qrow1 = qrow0 + 8 * D;
+    const float* qrow0 = q_s + (pb * 16 + g) * LD + t;
+    const float* qrow1 = qrow0 + 8 * LD;
 
     for (uint32_t tile = 0; tile < ntiles; ++tile) {
         cp_async_wait<kStages - 2>();
@@ -228,6 +233,8 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
         const float* kt = tiles + stage * 2 * kTileFloats;
         const float* vt = kt + kTileFloats;
         const int wrow0 = ksub * KW;  // this warp's first key row inside the tile
+        const float* kfrag = kt + (wrow0 + g) * LD + t;          // K fragment base: key row g, channel slot t
+        const float* vfrag = vt + (wrow0 + 2 * t) * LD + g;      // V fragment base: key row 2t, channel g
 
         // S(16 pairs x KW keys) = Q(16 x D) * K^T
         float s[KW / 8][4];
@@ -236,17 +243,17 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t ah[4], al[4];
-            const int c0 = ((2 * ks) ^ g) << 2, c1 = ((2 * ks + 1) ^ g) << 2;
-            split_tf32(qrow0[c0 + t], ah[0], al[0]);
-            split_tf32(qrow1[c0 + t], ah[1], al[1]);
-            split_tf32(qrow0[c1 + t], ah[2], al[2]);
-            split_tf32(qrow1[c1 + t], ah[3], al[3]);
+            const int c0 = 8 * ks, c1 = 8 * ks + 4;
+            split_tf32(qrow0[c0], ah[0], al[0]);
+            split_tf32(qrow1[c0], ah[1], al[1]);
+            split_tf32(qrow0[c1], ah[2], al[2]);
+            split_tf32(qrow1[c1], ah[3], al[3]);
 #pragma unroll
             for (int jn = 0; jn < KW / 8; ++jn) {
-                const float* krow = kt + (wrow0 + 8 * jn + g) * D;  // row & 7 == g
+                const float* krow = kfrag + 8 * jn * LD;
                 uint32_t bh[2], bl[2];
-                split_tf32(krow[c0 + t], bh[0], bl[0]);
-                split_tf32(krow[c1 + t], bh[1], bl[1]);
+                split_tf32(krow[c0], bh[0], bl[0]);
+                split_tf32(krow[c1], bh[1], bl[1]);
                 mma3(s[jn], ah, al, bh, bl);
             }
         }
@@ -312,15 +319,12 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
             split_tf32(p10, ph[1], pl[1]);
             split_tf32(p01, ph[2], pl[2]);
             split_tf32(p11, ph[3], pl[3]);
-            const int vr = wrow0 + 8 * kg + 2 * t;  // vr & 6 == (2t) & 6, the same for vr + 1
-            const float* vrow = vt + vr * D;
-            const int sw = (2 * t) & 6;
+            const float* vrow = vfrag + 8 * kg * LD;
 #pragma unroll
             for (int jn = 0; jn < NT; ++jn) {
-                const int off = (((2 * jn + (g >> 2)) ^ sw) << 2) + (g & 3);
                 uint32_t vh[2], vl[2];
-                split_tf32(vrow[off], vh[0], vl[0]);
-                split_tf32(vrow[D + off], vh[1], vl[1]);
+                split_tf32(vrow[8 * jn], vh[0], vl[0]);
+                split_tf32(vrow[LD + 8 * jn], vh[1], vl[1]);
                 mma3(o[jn], ph, pl, vh, vl);
             }
         }
@@ -383,20 +387,24 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
     __syncthreads();
     if (s_flag == 0) return;
     __threadfence();
-    // The last arrival merges every part of the block (log-sum-exp).  First the parts' weights per pair, into shared
-    // memory (the tiles' place): w[part][pair] = 2^(max_part - max_all) / sum; then every output channel as a
-    // weighted sum over the parts with all of a thread's loads of one part in flight together.
+    // The last arrival merges every part of the block (log-sum-exp).  First every part's (max, sum) pairs into shared
+    // memory in one round trip, from them the parts' weights per pair, w[part][pair] = 2^(max_part - max_all) / sum;
+    // then every output channel as a weighted sum over the parts, the loads of up to four parts in flight together.
     const float* all_o = p.part_o + cell * p.splits * PC * D;
     const float2* all_ml = reinterpret_cast<const float2*>(p.part_ml) + cell * p.splits * PC;
-    float* w_s = tiles;  // [parts][PC]
+    // (both arrays start where the queries were: at most kF32MaxParts x PC x 12 bytes, inside the CTA's allocation)
+    float* w_s = q_s;                                             // [parts][PC] weights
+    float2* ml_s = reinterpret_cast<float2*>(q_s + parts * PC);   // [parts][PC] (max, sum) pairs
+    static_assert(static_cast<size_t>(kF32MaxParts) * PC * 12 <= (static_cast<size_t>(PC) + kStages * 2 * kF32Tile) * LD * 4,
+                  "merge scratch exceeds the CTA's shared memory");
+    for (uint32_t i = tid; i < parts * PC; i += kF32Threads) ml_s[i] = __ldcg(all_ml + i);  // one round trip for all
+    __syncthreads();
     if (tid < cta_pairs) {
         float M = -INFINITY;
-#pragma unroll 8
-        for (uint32_t sp = 0; sp < parts; ++sp) M = fmaxf(M, __ldcg(all_ml + static_cast<size_t>(sp) * PC + tid).x);
+        for (uint32_t sp = 0; sp < parts; ++sp) M = fmaxf(M, ml_s[sp * PC + tid].x);
         float L = 0.f;
-#pragma unroll 8
         for (uint32_t sp = 0; sp < parts; ++sp) {
-            const float2 ml = __ldcg(all_ml + static_cast<size_t>(sp) * PC + tid);
+            const float2 ml = ml_s[sp * PC + tid];
             const float w = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - M);
             w_s[sp * PC + tid] = w;
             L += w * ml.y;
@@ -406,15 +414,31 @@ __device__ __forceinline__ void f32_block(const AttnLaunch& p, unsigned char* sm
     }
     __syncthreads();
     constexpr int kOutPerThread = PC * D / kF32Threads;
+    constexpr int kPartBatch = kOutPerThread <= 8 ? 4 : (kOutPerThread <= 16 ? 2 : 1);  // parts whose loads fly together
     float acc[kOutPerThread];
 #pragma unroll
     for (int i = 0; i < kOutPerThread; ++i) acc[i] = 0.f;
-    for (uint32_t sp = 0; sp < parts; ++sp) {
-        const float* src = all_o + static_cast<size_t>(sp) * PC * D;
+    for (uint32_t sp0 = 0; sp0 < parts; sp0 += kPartBatch) {
+        float v[kPartBatch][kOutPerThread];
 #pragma unroll
-        for (int i = 0; i < kOutPerThread; ++i) {
-            const uint32_t idx = tid + i * kF32Threads;
-            if (idx < cta_pairs * D) acc[i] += w_s[sp * PC + idx / D] * __ldcg(src + idx);
+        for (int b = 0; b < kPartBatch; ++b) {
+            const uint32_t sp = min(sp0 + b, parts - 1);  // a repeated part past the end gets weight zero below
+            const float* src = all_o + static_cast<size_t>(sp) * PC * D;
+#pragma unroll
+            for (int i = 0; i < kOutPerThread; ++i) {
+                const uint32_t idx = tid + i * kF32Threads;
+                v[b][i] = idx < cta_pairs * D ? __ldcg(src + idx) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < kPartBatch; ++b) {
+            const bool real = sp0 + b < parts;
+#pragma unroll
+            for (int i = 0; i < kOutPerThread; ++i) {
+                const uint32_t idx = tid + i * kF32Threads;
+                const float w = (real && idx < cta_pairs * D) ? w_s[(sp0 + b) * PC + idx / D] : 0.f;
+                acc[i] += w * v[b][i];
+            }
         }
     }
 #pragma unroll
@@ -442,7 +466,7 @@ __global__ void __launch_bounds__(kF32Threads, D == 64 ? 4 : 2) attn_f32_kernel(
 
 template <int D, int WK>
 constexpr size_t f32_smem_bytes() {
-    return (static_cast<size_t>(16 * (4 / WK)) * D + static_cast<size_t>(kF32Stages) * 2 * kF32Tile * D) * sizeof(float);
+    return (static_cast<size_t>(16 * (4 / WK)) * (D + 4) + static_cast<size_t>(kF32Stages) * 2 * kF32Tile * (D + 4)) * sizeof(float);
 }
 
 template <int D, int WK>
