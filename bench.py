@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--q-heads", type=int, default=None, help="override the query head count (shard studies)")
     ap.add_argument("--kv-heads", type=int, default=None, help="override the KV head count (shard studies)")
     ap.add_argument("--sequences", type=int, default=None, help="override the number of resident sequences")
+    ap.add_argument("--sessions", type=int, default=None, help="config 4 workloads: sessions on the shared prefix (default 16)")
+    ap.add_argument("--prefix-tokens", type=int, default=None, help="config 4 workloads: length of the shared prefix (default 2048)")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer directly instead of replaying a CUDA graph")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="N > 1: gather the head outputs with an NCCL all-gather per layer instead of inside the kernel")
@@ -642,6 +644,10 @@ def run_ours(args):
         if env.world != 1:
             line = {"unavailable": "this workload is measured on one GPU"} if env.rank == 0 else None
         else:
+            if args.sessions:
+                bench_paths.SESSIONS = args.sessions
+            if args.prefix_tokens:
+                bench_paths.PREFIX = args.prefix_tokens
             line = bench_paths.RUNNERS[args.workload](args, ClockSampler, short=False)
     check = (line or {}).get("gather_check")
     if check is not None and not check["ok"]:

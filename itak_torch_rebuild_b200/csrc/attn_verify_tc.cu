@@ -753,32 +753,72 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
             if (*s_flag != 0) {  // the last CTA of the cell merges every split
                 __threadfence();
                 const float* all_o = p.part_o + cell * p.splits * PC * D;
-                const float* all_ml = p.part_ml + cell * p.splits * PC * 2;
+                const float2* all_ml = reinterpret_cast<const float2*>(p.part_ml) + cell * p.splits * PC;
                 const uint32_t cta_pairs = min(static_cast<uint32_t>(PC), n_pairs - pc * PC);
-                for (uint32_t idx = tid; idx < cta_pairs * (D / 4); idx += kTcSoftmaxThreads) {
-                    const uint32_t q = idx / (D / 4), d4 = idx % (D / 4);
+                // Every split's (max, sum) pairs come into shared memory in one round trip (the rings are idle: at
+                // most 256 splits x PC x 12 bytes), the splits' weights per pair follow from them, and every output
+                // is a weighted sum with all of a thread's loads of one split (two, on a 32-pair block) in flight
+                // together - not one dependent round trip per split and output.
+                softmax_sync();  // the staging rows above have been read by every thread
+                float* w_s = reinterpret_cast<float*>(smem);                 // [splits][PC]
+                float2* ml_s = reinterpret_cast<float2*>(w_s + p.splits * PC);  // [splits][PC]
+                for (uint32_t i = tid; i < p.splits * PC; i += kTcSoftmaxThreads) ml_s[i] = __ldcg(all_ml + i);
+                softmax_sync();
+                if (static_cast<uint32_t>(tid) < cta_pairs) {
                     float Mx = -INFINITY;
-                    for (uint32_t s = 0; s < p.splits; ++s)
-                        Mx = fmaxf(Mx, __ldcg(all_ml + (static_cast<size_t>(s) * PC + q) * 2));
+                    for (uint32_t s = 0; s < p.splits; ++s) Mx = fmaxf(Mx, ml_s[s * PC + tid].x);
                     float Ls = 0.f;
-                    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (uint32_t s = 0; s < p.splits; ++s) {
-                        const float ms = __ldcg(all_ml + (static_cast<size_t>(s) * PC + q) * 2);
-                        if (ms == -INFINITY) continue;
-                        const float ws = fast_exp2(ms - Mx);
-                        Ls += ws * __ldcg(all_ml + (static_cast<size_t>(s) * PC + q) * 2 + 1);
-                        const float4 v =
-                            __ldcg(reinterpret_cast<const float4*>(all_o + (static_cast<size_t>(s) * PC + q) * D) + d4);
-                        o.x += ws * v.x;
-                        o.y += ws * v.y;
-                        o.z += ws * v.z;
-                        o.w += ws * v.w;
+                        const float2 ml = ml_s[s * PC + tid];
+                        const float ws = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - Mx);
+                        w_s[s * PC + tid] = ws;
+                        Ls += ws * ml.y;
                     }
-                    const uint32_t gp = pc * PC + q;
-                    const uint32_t orow = gp / nh, h = gp % nh;
                     const float inv = 1.f / Ls;
-                    reinterpret_cast<float4*>(p.out + ((static_cast<size_t>(seq) * p.rows + orow) * p.q_heads + head0 + h) *
-                                                          D)[d4] = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+                    for (uint32_t s = 0; s < p.splits; ++s) w_s[s * PC + tid] *= inv;
+                }
+                softmax_sync();
+                constexpr int kOut4 = PC * (D / 4) / kTcSoftmaxThreads;  // float4 outputs per thread: 8 or 16
+                constexpr int kSplitBatch = kOut4 <= 8 ? 2 : 1;
+                float4 o[kOut4];
+#pragma unroll
+                for (int i = 0; i < kOut4; ++i) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t s0 = 0; s0 < p.splits; s0 += kSplitBatch) {
+                    float4 v[kSplitBatch][kOut4];
+#pragma unroll
+                    for (int bb = 0; bb < kSplitBatch; ++bb) {
+                        const uint32_t s = min(s0 + bb, p.splits - 1);  // a repeated split past the end weighs zero
+                        const float4* src = reinterpret_cast<const float4*>(all_o + static_cast<size_t>(s) * PC * D);
+#pragma unroll
+                        for (int i = 0; i < kOut4; ++i) {
+                            const uint32_t idx = tid + i * kTcSoftmaxThreads;
+                            v[bb][i] = idx < cta_pairs * (D / 4) ? __ldcg(src + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+#pragma unroll
+                    for (int bb = 0; bb < kSplitBatch; ++bb) {
+                        const bool real = s0 + bb < p.splits;
+#pragma unroll
+                        for (int i = 0; i < kOut4; ++i) {
+                            const uint32_t idx = tid + i * kTcSoftmaxThreads;
+                            const float ws = (real && idx < cta_pairs * (D / 4)) ? w_s[(s0 + bb) * PC + idx / (D / 4)] : 0.f;
+                            o[i].x += ws * v[bb][i].x;
+                            o[i].y += ws * v[bb][i].y;
+                            o[i].z += ws * v[bb][i].z;
+                            o[i].w += ws * v[bb][i].w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kOut4; ++i) {
+                    const uint32_t idx = tid + i * kTcSoftmaxThreads;
+                    if (idx < cta_pairs * (D / 4)) {
+                        const uint32_t q = idx / (D / 4), d4 = idx % (D / 4);
+                        const uint32_t gp = pc * PC + q;
+                        const uint32_t orow = gp / nh, h = gp % nh;
+                        reinterpret_cast<float4*>(p.out + ((static_cast<size_t>(seq) * p.rows + orow) * p.q_heads + head0 + h) *
+                                                              D)[d4] = o[i];
+                    }
                 }
                 if (tid == 0) p.tickets[cell] = 0u;
             }
