@@ -256,24 +256,85 @@ __global__ void __launch_bounds__(kVerThreads, 2) verify_f16_kernel(const __grid
     const float* all_o = p.part_o + cell * p.splits * kPairsPerCta * D;
     const float* all_ml = p.part_ml + cell * p.splits * kPairsPerCta * 2;
     const uint32_t cta_pairs = min(static_cast<uint32_t>(kPairsPerCta), n_pairs - pc * kPairsPerCta);
-    for (uint32_t idx = tid; idx < cta_pairs * D; idx += kVerThreads) {
-        const uint32_t q = idx / D, dd = idx % D;
-        float M = -INFINITY, L = 0.f, O = 0.f;
-        for (uint32_t s = 0; s < p.splits; ++s) {
-            const float ms = __ldcg(all_ml + (static_cast<size_t>(s) * kPairsPerCta + q) * 2);
-            if (ms == -INFINITY) continue;
-            const float ls = __ldcg(all_ml + (static_cast<size_t>(s) * kPairsPerCta + q) * 2 + 1);
-            const float os = __ldcg(all_o + (static_cast<size_t>(s) * kPairsPerCta + q) * D + dd);
-            const float Mn = fmaxf(M, ms);
-            const float a = fast_exp2(M - Mn);
-            const float b = fast_exp2(ms - Mn);
-            O = O * a + os * b;
-            L = L * a + ls * b;
-            M = Mn;
+    constexpr uint32_t kSmemBytes = kVerStages * 2 * kTileBytes;
+    if (p.splits * kPairsPerCta * 12u <= kSmemBytes) {
+        // Every split's (max, sum) pairs come into shared memory in one round trip (the tile stages are idle), the
+        // splits' weights per pair follow from them, and every output is a weighted sum over the splits with all of a
+        // thread's loads of one split (two, at head_dim 64) in flight - not one dependent round trip per split and output.
+        float* w_s = reinterpret_cast<float*>(smem);                               // [splits][32]
+        float2* ml_s = reinterpret_cast<float2*>(w_s + p.splits * kPairsPerCta);  // [splits][32]
+        const float2* ml2 = reinterpret_cast<const float2*>(all_ml);
+        for (uint32_t i = tid; i < p.splits * kPairsPerCta; i += kVerThreads) ml_s[i] = __ldcg(ml2 + i);
+        __syncthreads();
+        if (static_cast<uint32_t>(tid) < cta_pairs) {
+            float M = -INFINITY;
+            for (uint32_t s = 0; s < p.splits; ++s) M = fmaxf(M, ml_s[s * kPairsPerCta + tid].x);
+            float L = 0.f;
+            for (uint32_t s = 0; s < p.splits; ++s) {
+                const float2 ml = ml_s[s * kPairsPerCta + tid];
+                const float w = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - M);
+                w_s[s * kPairsPerCta + tid] = w;
+                L += w * ml.y;
+            }
+            const float inv = 1.f / L;
+            for (uint32_t s = 0; s < p.splits; ++s) w_s[s * kPairsPerCta + tid] *= inv;
         }
-        const uint32_t gp = pc * kPairsPerCta + q;
-        const uint32_t r = gp / nh, h = gp % nh;
-        p.out[((static_cast<size_t>(seq) * p.rows + r) * p.q_heads + head0 + h) * D + dd] = O / L;
+        __syncthreads();
+        constexpr int kOut = kPairsPerCta * D / kVerThreads;  // outputs per thread: 16 or 32
+        constexpr int kBatch = kOut <= 16 ? 2 : 1;  // (kept small: the epilogue must not raise the kernel's register count)
+        float acc[kOut];
+#pragma unroll
+        for (int i = 0; i < kOut; ++i) acc[i] = 0.f;
+        for (uint32_t s0 = 0; s0 < p.splits; s0 += kBatch) {
+            float v[kBatch][kOut];
+#pragma unroll
+            for (int bb = 0; bb < kBatch; ++bb) {
+                const uint32_t s = min(s0 + bb, p.splits - 1);  // a repeated split past the end weighs zero
+                const float* src = all_o + static_cast<size_t>(s) * kPairsPerCta * D;
+#pragma unroll
+                for (int i = 0; i < kOut; ++i) {
+                    const uint32_t idx = tid + i * kVerThreads;
+                    v[bb][i] = idx < cta_pairs * D ? __ldcg(src + idx) : 0.f;
+                }
+            }
+#pragma unroll
+            for (int bb = 0; bb < kBatch; ++bb) {
+                const bool real = s0 + bb < p.splits;
+#pragma unroll
+                for (int i = 0; i < kOut; ++i) {
+                    const uint32_t idx = tid + i * kVerThreads;
+                    acc[i] += ((real && idx < cta_pairs * D) ? w_s[(s0 + bb) * kPairsPerCta + idx / D] : 0.f) * v[bb][i];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kOut; ++i) {
+            const uint32_t idx = tid + i * kVerThreads;
+            if (idx < cta_pairs * D) {
+                const uint32_t gp = pc * kPairsPerCta + idx / D;
+                p.out[((static_cast<size_t>(seq) * p.rows + gp / nh) * p.q_heads + head0 + gp % nh) * D + idx % D] = acc[i];
+            }
+        }
+    } else {
+        for (uint32_t idx = tid; idx < cta_pairs * D; idx += kVerThreads) {
+            const uint32_t q = idx / D, dd = idx % D;
+            float M = -INFINITY, L = 0.f, O = 0.f;
+            for (uint32_t s = 0; s < p.splits; ++s) {
+                const float ms = __ldcg(all_ml + (static_cast<size_t>(s) * kPairsPerCta + q) * 2);
+                if (ms == -INFINITY) continue;
+                const float ls = __ldcg(all_ml + (static_cast<size_t>(s) * kPairsPerCta + q) * 2 + 1);
+                const float os = __ldcg(all_o + (static_cast<size_t>(s) * kPairsPerCta + q) * D + dd);
+                const float Mn = fmaxf(M, ms);
+                const float a = fast_exp2(M - Mn);
+                const float b = fast_exp2(ms - Mn);
+                O = O * a + os * b;
+                L = L * a + ls * b;
+                M = Mn;
+            }
+            const uint32_t gp = pc * kPairsPerCta + q;
+            const uint32_t r = gp / nh, h = gp % nh;
+            p.out[((static_cast<size_t>(seq) * p.rows + r) * p.q_heads + head0 + h) * D + dd] = O / L;
+        }
     }
     if (tid == 0) p.tickets[cell] = 0u;
 }
