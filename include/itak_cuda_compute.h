@@ -150,7 +150,7 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * first launch starts behind the first, in per cent of the time the first needs to stream its keys; default 100),
  * "layers_host_bulk_bytes" (itk_attention_layers_host: a forward that uploads no more than this many bytes sends
  * all layers' rows up in three copies, launches the layers back to back and brings the results down in one copy,
- * instead of pipelining per-layer copies against the kernels; default 4 MiB, 0 = always pipeline).
+ * instead of pipelining per-layer copies against the kernels; default 1 MiB (where a layer's kernel is shorter than its copies' fixed cost), 0 = always pipeline).
  * Unknown names and out-of-range values are refused; not allowed inside
  * a resident loop. */
 int itk_set_option(itk_backend* b, const char* name, int64_t value);

@@ -107,7 +107,7 @@ struct itk_backend {
     int sm_count = 148;
     int forced_splits = 0;
     int forced_ctas = 0;         // option decode_ctas: persistent CTAs of the decode kernel (default 2 per SM)
-    uint64_t fw_bulk_bytes = 4ull << 20;  // option layers_host_bulk_bytes: forwards that upload no more take the bulk path
+    uint64_t fw_bulk_bytes = 1ull << 20;  // option layers_host_bulk_bytes: forwards that upload no more take the bulk path
     bool separate_append = false;  // option separate_append = 1: decode steps launch the append kernel separately
     bool force_general = false;  // option force_general = 1: multi-row launches take the CUDA-core kernel (A/B checks)
     bool verify_tc = true;       // option verify_tc = 0: multi-row launches take the mma.sync kernel instead of tcgen05
