@@ -151,6 +151,10 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * "layers_host_bulk_bytes" (itk_attention_layers_host: a forward that uploads no more than this many bytes sends
  * all layers' rows up in three copies, launches the layers back to back and brings the results down in one copy,
  * instead of pipelining per-layer copies against the kernels; default 1 MiB (where a layer's kernel is shorter than its copies' fixed cost), 0 = always pipeline).
+ * "tc_wait_kclocks" (bound of every wait inside the tcgen05 multi-row kernel, in units of 1024 SM clocks; 0 = the
+ * default of about a second) and "tc_withhold_first_tile" (for tests of that kernel's give-up path only: the first
+ * key tile of every CTA is loaded but never reported, so the wait for it runs out, every role leaves its loop, the
+ * launch's outputs are not valid and the next synchronising call returns ITK_ERR_CUDA; default 0).
  * Unknown names and out-of-range values are refused; not allowed inside
  * a resident loop. */
 int itk_set_option(itk_backend* b, const char* name, int64_t value);

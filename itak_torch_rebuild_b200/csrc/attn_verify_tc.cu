@@ -108,8 +108,9 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar_addr) {
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 // Bounded wait; a wait that runs out raises the CTA's abort flag, which every role polls once per tile.
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag) {
-    if (tc::mbar_wait_bounded(bar_addr, parity, kWaitClocks)) return true;
+__device__ __forceinline__ bool wait_or_abort_within(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag,
+                                                     long long limit_clocks) {
+    if (tc::mbar_wait_bounded(bar_addr, parity, limit_clocks)) return true;
     *abort_flag = 1;
     return false;
 }
@@ -200,6 +201,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
     // writes them - while every thread that touches the queries, the call's new rows, the scratch or the outputs
     // waits first.
     const bool early_kv = p.pdl == 2;
+    const long long wait_clocks = p.tc_wait_kclocks != 0 ? static_cast<long long>(p.tc_wait_kclocks) << 10 : kWaitClocks;
+    auto wait_or_abort = [wait_clocks](uint32_t bar_addr, uint32_t parity, volatile int* flag) {
+        return wait_or_abort_within(bar_addr, parity, flag, wait_clocks);
+    };
     if (p.pdl == 1) asm volatile("griddepcontrol.wait;\n" ::: "memory");
     if (p.pdl != 0) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // The query rows are requested first of all (each softmax warp a quarter of the CTA's PC distinct rows, lane l
@@ -280,6 +285,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
         const int64_t new_rel = static_cast<int64_t>(sd.q_pos0) - (static_cast<int64_t>(sd.kv_lo) + k0);
         // the CTAs of the LAST pair block see every row of the launch: they are the ones that store them
         const bool stores_new = gc == 0 && pc == pchunks - 1;
+        // (tests of the give-up path: the first K tile lands but is never reported)
+        auto withheld = [&](uint32_t tile) { return p.tc_withhold != 0 && !is_v && tile == 0; };
         bool waited = !early_kv;  // (early start) has this loader thread waited for the predecessor yet
         // Before the query rows have left their staging area (the last V stage): an ordinary launch requests only the
         // first K tile (see below); an early one fills the K ring and all V stages but the last.
@@ -382,7 +389,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                 }
                 cp_async_wait_all();
                 tc::fence_proxy_async();  // plain stores into the stage: visible to the tensor core before the arrival
-                mbar_arrive(bar_full + 8 * st);
+                if (!withheld(tile)) mbar_arrive(bar_full + 8 * st);
                 continue;
             }
             uint32_t sr0 = s0 + row0;
@@ -416,7 +423,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) verify_tc_kernel(const __grid_c
                 }
             }
             // The stage's full barrier receives this thread's arrival when the copies above have landed; nobody waits.
-            cp_async_arrive_noinc(bar_full + 8 * st);
+            if (!withheld(tile)) cp_async_arrive_noinc(bar_full + 8 * st);
             if (lt == 0) TC_TRACE(p, tile * 8 + (is_v ? 6 : 5));
         }
         cp_async_wait_all();

@@ -107,6 +107,8 @@ struct itk_backend {
     int sm_count = 148;
     int forced_splits = 0;
     int forced_ctas = 0;         // option decode_ctas: persistent CTAs of the decode kernel (default 2 per SM)
+    uint32_t tc_wait_kclocks = 0;  // option tc_wait_kclocks: bound of the tcgen05 kernel's waits (0 = default)
+    bool tc_withhold = false;      // option tc_withhold_first_tile: tests of the give-up path
     uint64_t fw_bulk_bytes = 1ull << 20;  // option layers_host_bulk_bytes: forwards that upload no more take the bulk path
     bool separate_append = false;  // option separate_append = 1: decode steps launch the append kernel separately
     bool force_general = false;  // option force_general = 1: multi-row launches take the CUDA-core kernel (A/B checks)
@@ -409,6 +411,8 @@ int run_attention(itk_backend* b, uint32_t layer, uint32_t n, const SeqDesc* seq
                 p.v_new = d_v_new + static_cast<size_t>(at) * rows * b->row_len();
             }
             b->status_pending = true;
+            p.tc_wait_kclocks = b->tc_wait_kclocks;
+            p.tc_withhold = b->tc_withhold ? 1u : 0u;
             // behind an unbroken run of this kernel's launches on other layers, the K/V stream may start early
             const bool early = b->use_pdl && b->tc_chain_live && layer < 64 && ((b->tc_chain_mask >> layer) & 1ull) == 0 &&
                                b->prof_events.empty();
@@ -852,6 +856,12 @@ int itk_set_option(itk_backend* b, const char* name, int64_t value) {
         b->gth_poll_limit = static_cast<uint32_t>(value);
         return ITK_OK;
     }
+    if (key == "tc_wait_kclocks") {
+        if (value < 0 || value > (1ll << 22)) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: tc_wait_kclocks must be 0..2^22");
+        b->tc_wait_kclocks = static_cast<uint32_t>(value);
+        return ITK_OK;
+    }
+    if (key == "tc_withhold_first_tile") return flag(&b->tc_withhold);
     if (key == "layers_host_bulk_bytes") {
         if (value < 0 || value > (1ll << 40)) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: layers_host_bulk_bytes must be 0..2^40");
         b->fw_bulk_bytes = static_cast<uint64_t>(value);

@@ -122,6 +122,10 @@ struct AttnLaunch {
                              // words: whole batch, lane 0, lane 1); null = every CTA works it out itself
     unsigned int* status;    // device word the kernels OR error bits into (bit 0: a bounded wait on the tensor
                              // core ran out in the tcgen05 multi-row kernel); may be null
+    uint32_t tc_wait_kclocks;  // tcgen05 multi-row kernel: limit of every bounded wait in units of 1024 SM clocks
+                               // (0 = the default of about a second)
+    uint32_t tc_withhold;      // tcgen05 multi-row kernel, tests of the give-up path only: 1 = the K loader never
+                               // reports the first tile, so the first wait for it runs out and every role leaves
     float scale;             // score scale, 1/sqrt(D) by default
 #ifdef ITK_DECODE_TRACE
     unsigned long long* trace;  // timeline build only: [cta][16] %globaltimer stamps of the decode kernel's phases

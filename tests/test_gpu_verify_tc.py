@@ -163,3 +163,37 @@ def test_agrees_with_the_mma_sync_kernel_on_batched_sessions():
         outs.append(gpu.attention_batch(0, list(range(len(lens))), lens, rows, q, k, v))
         gpu.synchronize()
     assert attention_error(outs[0], outs[1], hq, D) < 1e-5
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_succeeds():
+    """Every wait inside the kernel is bounded.  With the first key tile of every CTA loaded but never reported (a test
+    switch) and the bound set to about a millisecond, the wait for that tile runs out: every role leaves its loop, the
+    kernel returns, the call that synchronises is refused by name - and the backend goes on working: the same slot,
+    reset and refilled, matches the oracle again.  Nothing faults and nothing hangs."""
+    from itak_torch_rebuild_b200 import CudaComputeError, _lib
+
+    hq, hkv, n0, rows = 32, 8, 300, 7
+    gpu, refs = build([0], hq, hkv, n0, rows, env={"tc_wait_kclocks": 2000, "tc_withhold_first_tile": 1}, seed=41)
+    rng = np.random.default_rng(42)
+    pos = PositionCache()
+    pos.advance(n0)
+    q = rng.standard_normal((rows, hq * D)).astype(np.float32)
+    k = rng.standard_normal((rows, hkv * D)).astype(np.float32)
+    v = rng.standard_normal((rows, hkv * D)).astype(np.float32)
+    with pytest.raises(CudaComputeError) as e:
+        gpu.attention(0, q, k, v, pos)
+    assert e.value.code == _lib.ERR_CUDA and "bounded wait" in e.value.msg
+    gpu.set_option("tc_withhold_first_tile", 0)
+    gpu.set_option("tc_wait_kclocks", 0)
+    # what the refused launch left in the slot is not defined: the sequence starts again
+    gpu.reset(0)
+    rng = np.random.default_rng(43)
+    k0 = rng.standard_normal((n0, hkv * D)).astype(np.float32)
+    v0 = rng.standard_normal((n0, hkv * D)).astype(np.float32)
+    gpu.append_rows(0, k0, v0, 0)
+    ref = orc.KvCache([orc.GLOBAL], hkv, D)
+    ref.append_rows(0, stored(k0, DTYPE), stored(v0, DTYPE), 0)
+    worst, _ = run_blocks(gpu, [ref], [0], hq, hkv, n0, rows, blocks=2, seed=44)
+    assert worst <= TIGHT
+    assert_view_equal(gpu, ref, 0, DTYPE)
+    gpu.close()
