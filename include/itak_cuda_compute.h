@@ -151,6 +151,9 @@ int itk_set_stream(itk_backend* b, void* cuda_stream);
  * "layers_host_bulk_bytes" (itk_attention_layers_host: a forward that uploads no more than this many bytes sends
  * all layers' rows up in three copies, launches the layers back to back and brings the results down in one copy,
  * instead of pipelining per-layer copies against the kernels; default 1 MiB (where a layer's kernel is shorter than its copies' fixed cost), 0 = always pipeline).
+ * "layers_host_decode_loop" (itk_attention_layers_host: a decode step - one row per sequence on an f16 cache - that
+ * uploads no more than this many bytes runs as one step of the replayable loop behind three strided uploads;
+ * default 8 MiB, 0 = never),
  * "tc_wait_kclocks" (bound of every wait inside the tcgen05 multi-row kernel, in units of 1024 SM clocks; 0 = the
  * default of about a second) and "tc_withhold_first_tile" (for tests of that kernel's give-up path only: the first
  * key tile of every CTA is loaded but never reported, so the wait for it runs out, every role leaves its loop, the
@@ -196,8 +199,9 @@ int itk_attention_batch(itk_backend* b, uint32_t layer, uint32_t n_seqs, const u
  * on the host (a benchmark of the path alone, a replay of recorded activations): host q [layers][n_seqs][rows][q_heads*D],
  * k, v [layers][n_seqs][rows][kv_heads*D], out like q; every slot must sit at positions[i] on every layer.  The
  * backend pipelines the layers over three streams - layer l's rows upload while layer l-1 computes and layer l-2's
- * result downloads - and returns after the last result is in `out`; a small forward (see the option
- * "layers_host_bulk_bytes") instead sends every layer's rows up in three strided copies, launches the layers back to
+ * result downloads - and returns after the last result is in `out`; a decode step on an f16 cache that moves little
+ * (option "layers_host_decode_loop") runs as one step of the replayable loop (itk_resident_begin / layer / end) behind three strided uploads; another small forward (option
+ * "layers_host_bulk_bytes") sends every layer's rows up in three strided copies, launches the layers back to
  * back and brings all results down in one copy, since per-layer copies would cost more than their overlap hides.  Same refusals as itk_attention_batch, all
  * layers validated before anything is queued.  The first call allocates the per-layer staging.  No counterpart in
  * the reference, whose forward calls Compute::attention layer by layer (crates/muse-glimmer/src/model.rs:452-462). */

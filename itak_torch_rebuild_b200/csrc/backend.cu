@@ -109,6 +109,7 @@ struct itk_backend {
     int forced_ctas = 0;         // option decode_ctas: persistent CTAs of the decode kernel (default 2 per SM)
     uint32_t tc_wait_kclocks = 0;  // option tc_wait_kclocks: bound of the tcgen05 kernel's waits (0 = default)
     bool tc_withhold = false;      // option tc_withhold_first_tile: tests of the give-up path
+    uint64_t fw_loop_bytes = 8ull << 20;  // option layers_host_decode_loop: decode steps from host buffers that upload no more run as one step of the replayable loop
     uint64_t fw_bulk_bytes = 1ull << 20;  // option layers_host_bulk_bytes: forwards that upload no more take the bulk path
     bool separate_append = false;  // option separate_append = 1: decode steps launch the append kernel separately
     bool force_general = false;  // option force_general = 1: multi-row launches take the CUDA-core kernel (A/B checks)
@@ -862,6 +863,11 @@ int itk_set_option(itk_backend* b, const char* name, int64_t value) {
         return ITK_OK;
     }
     if (key == "tc_withhold_first_tile") return flag(&b->tc_withhold);
+    if (key == "layers_host_decode_loop") {
+        if (value < 0 || value > (1ll << 40)) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: layers_host_decode_loop must be 0..2^40");
+        b->fw_loop_bytes = static_cast<uint64_t>(value);
+        return ITK_OK;
+    }
     if (key == "layers_host_bulk_bytes") {
         if (value < 0 || value > (1ll << 40)) return b->fail(ITK_ERR_INVALID_ARGUMENT, "set_option: layers_host_bulk_bytes must be 0..2^40");
         b->fw_bulk_bytes = static_cast<uint64_t>(value);
@@ -1461,11 +1467,41 @@ int itk_attention_layers_host(itk_backend* b, uint32_t n_seqs, const uint32_t* s
     }
     const size_t qn = total_rows * b->q_width(), kn = total_rows * b->row_len();
     const size_t qs = b->fw_rows * b->q_width(), ks = b->fw_rows * b->row_len();  // per-layer staging strides
+    const size_t f = sizeof(float);
+    if (rows == 1 && b->f16 && itk::decode_f16_supported(b->cfg.head_dim, 1) && !b->res_active &&
+        static_cast<uint64_t>(L) * (qn + 2 * kn) * f <= b->fw_loop_bytes) {
+        // A decode step from host buffers: every layer's rows go up in three strided copies and the step runs as one
+        // step of the replayable loop - positions on the device, each layer's launch a programmatic dependent of the
+        // one before, two lanes on short launches - instead of as ordinary per-layer launches behind per-layer copies
+        // (whose fixed cost exceeds a short layer's kernel time, above all with one process per GPU on a shared host).
+        // A step that moves more than fw_loop_bytes gains more from copies that overlap the kernels.
+        ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_q, qs * f, q, qn * f, qn * f, L, cudaMemcpyHostToDevice, b->stream), "q upload");
+        ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_k, ks * f, k, kn * f, kn * f, L, cudaMemcpyHostToDevice, b->stream), "k upload");
+        ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_v, ks * f, v, kn * f, kn * f, L, cudaMemcpyHostToDevice, b->stream), "v upload");
+        int rc = itk_resident_begin(b, n_seqs, slots, 1);
+        if (rc == ITK_OK) {
+            for (uint32_t l = 0; l < L && rc == ITK_OK; ++l)
+                rc = resident_layer_impl(b, l, b->fw_q + l * qs, b->fw_k + l * ks, b->fw_v + l * ks, b->fw_out + l * qs, false, 0);
+            const int rc_end = itk_resident_end(b, rc == ITK_OK ? 1 : 0);
+            if (rc != ITK_OK) return rc;
+            if (rc_end != ITK_OK) return rc_end;
+        } else {
+            // the loop's own limits (its scratch, a live checkpoint's range): the step runs as ordinary launches
+            for (uint32_t l = 0; l < L; ++l)
+                if (int rc2 = step_device(b, l, n_seqs, slots, positions, rows, b->fw_q + l * qs, b->fw_k + l * ks,
+                                          b->fw_v + l * ks, b->fw_out + l * qs))
+                    return rc2;
+        }
+        ITK_CUDA(b, cudaMemcpy2DAsync(out, qn * f, b->fw_out, qs * f, qn * f, L, cudaMemcpyDeviceToHost, b->stream),
+                 "output download");
+        queue_status_read(b);
+        ITK_CUDA(b, cudaStreamSynchronize(b->stream), "forward");
+        return check_status(b);
+    }
     if (static_cast<uint64_t>(L) * (qn + 2 * kn) * sizeof(float) <= b->fw_bulk_bytes) {
         // A small forward (a decode step of a few sequences): the per-layer copies' fixed cost would outweigh what
         // their overlap with the kernels hides.  Every layer's rows go up in three strided copies, the layers'
         // launches follow back to back, one strided copy brings all results down.
-        const size_t f = sizeof(float);
         ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_q, qs * f, q, qn * f, qn * f, L, cudaMemcpyHostToDevice, b->stream), "q upload");
         ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_k, ks * f, k, kn * f, kn * f, L, cudaMemcpyHostToDevice, b->stream), "k upload");
         ITK_CUDA(b, cudaMemcpy2DAsync(b->fw_v, ks * f, v, kn * f, kn * f, L, cudaMemcpyHostToDevice, b->stream), "v upload");
