@@ -577,8 +577,12 @@ def measure_decode(args, env: Dist, workload, geom, steps, warmup, *, e2e=True, 
         d2h = layers * seqs * hq_l * d * 4 * world
         e2e_rec = {"value": 1.0 / whole_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                    "steps": e2e_steps,
-                   "call": "itk_attention_layers_host: one call per step, pinned host q/k/v/out of all layers, uploads / "
-                           "kernels / downloads of consecutive layers overlapped, returns with the step's result on the host",
+                   "call": "itk_attention_layers_host: one call per step, pinned host q/k/v/out of all layers, returns with "
+                           "the step's result on the host; "
+                           + ("uploads / kernels / downloads of consecutive layers overlapped on three streams"
+                              if h2d // world > (8 << 20) else
+                              "a step of 8 MiB or less: three strided uploads, the step as one step of the replayable "
+                              "loop, one strided download"),
                    "per_layer_call": {"value": 1.0 / layer_s, "unit": UNIT, "steps": 3,
                                       "call": "itk_attention_batch per layer (the reference's Compute::attention shape): "
                                               "H2D, kernel, D2H and a synchronisation every layer"},
