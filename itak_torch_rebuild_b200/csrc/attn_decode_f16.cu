@@ -522,8 +522,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
         }
 
         if (cc.tile + 1 == cc.T || i + 1 == ntiles) {
-            // This CTA's part of the cell is complete: merge the 4 warps through shared memory, 32 channels at
-            // a time, then hand the (m, l, o) part to the cell's merge.
+            // This CTA's part of the cell is complete: merge the 4 warps through shared memory, then hand the
+            // (m, l, o) part to the cell's merge.
             float lq = l + __shfl_xor_sync(0xffffffffu, l, 1);
             lq += __shfl_xor_sync(0xffffffffu, lq, 2);
             if (i + 1 == ntiles) ITK_TRACE(p, 5);
@@ -532,11 +532,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                 wm[warp * kHeadsPerCta + g] = m;
                 wl[warp * kHeadsPerCta + g] = lq;
             }
-            if (i + 1 == ntiles) {
-                // End of the run: every staged tile has been consumed, so the pipeline's shared memory is free and
-                // the four warps exchange whole rows at once (row stride D + 8 floats: conflict-free both ways).
+            {
+                // The stage this tile was read from is free until the next iteration refills it (the barrier above
+                // means every warp is done with it; the loads in flight target the other stages): the four warps
+                // exchange whole rows through it at once (row stride D + 8 floats: conflict-free both ways).
                 constexpr int RS = D + 8;
-                float* big = reinterpret_cast<float*>(smem);  // [4][8][RS]
+                static_assert(kDecodeWarps * kHeadsPerCta * RS * 4 <= kDecodeWarps * 2 * kSliceBytes, "exchange rows exceed a stage");
+                float* big = reinterpret_cast<float*>(smem + (i % STAGES) * (kDecodeWarps * 2 * kSliceBytes));  // [4][8][RS]
                 float* dst = big + (warp * kHeadsPerCta + g) * RS + 2 * t;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
@@ -557,35 +559,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
                         }
                     }
                     fo[idx] = O;
-                }
-            } else {
-#pragma unroll
-                for (int ps = 0; ps < D / 32; ++ps) {
-                    float* dst = wpart + (warp * kHeadsPerCta + g) * 32;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int nt = 4 * ps + j;
-                        *reinterpret_cast<float2*>(dst + 8 * j + 2 * t) =
-                            make_float2(o[nt][0] + o[nt][2], o[nt][1] + o[nt][3]);
-                    }
-                    __syncthreads();
-                    for (int idx = tid; idx < kHeadsPerCta * 32; idx += kDecodeThreads) {
-                        const int h = idx >> 5, c = idx & 31;
-                        float M = -INFINITY;
-#pragma unroll
-                        for (int w = 0; w < kDecodeWarps; ++w) M = fmaxf(M, wm[w * kHeadsPerCta + h]);
-                        float O = 0.f;
-                        if (M != -INFINITY) {
-#pragma unroll
-                            for (int w = 0; w < kDecodeWarps; ++w) {
-                                const float mw = wm[w * kHeadsPerCta + h];
-                                const float a = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
-                                O += a * wpart[(w * kHeadsPerCta + h) * 32 + c];
-                            }
-                        }
-                        fo[h * D + 32 * ps + c] = O;
-                    }
-                    __syncthreads();
                 }
             }
             if (tid < kHeadsPerCta) {
