@@ -135,10 +135,10 @@ __host__ __device__ constexpr size_t decode_pipe_bytes() {
 }
 template <int D, int STAGES>
 constexpr size_t decode_smem_bytes() {
-    // pipeline + warp-merge staging [4][8][32] + fo[8][D] + wm/wl[4][8] x2 + fm, fl + flag pad + merge weights
-    // + cumulative tile table
+    // pipeline (its stage just consumed doubles as the warps' exchange area at a cell end) + fo[8][D]
+    // + wm/wl[4][8] x2 + fm, fl + flag pad + merge weights + cumulative tile table
     return decode_pipe_bytes<D, STAGES>() +
-           (kDecodeWarps * kHeadsPerCta * 32 + kHeadsPerCta * D + 2 * kDecodeWarps * kHeadsPerCta + 2 * kHeadsPerCta + 4 +
+           (kHeadsPerCta * D + 2 * kDecodeWarps * kHeadsPerCta + 2 * kHeadsPerCta + 4 +
             2 * kDecodeMaxParts * kHeadsPerCta + kHeadsPerCta + kPlanWords) * sizeof(float);
 }
 
@@ -151,8 +151,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_f16_kernel(const __g
     constexpr int KS = D / 16;                   // k-steps of the QK^T product
     constexpr int NT = D / 8;                    // n-tiles of the PV product
 
-    float* wpart = reinterpret_cast<float*>(smem + decode_pipe_bytes<D, STAGES>());  // [4][8][32]
-    float* fo = wpart + kDecodeWarps * kHeadsPerCta * 32;                            // [8][D]
+    float* fo = reinterpret_cast<float*>(smem + decode_pipe_bytes<D, STAGES>());      // [8][D]
     float* wm = fo + kHeadsPerCta * D;                                               // [4][8]
     float* wl = wm + kDecodeWarps * kHeadsPerCta;                                    // [4][8]
     float* fm = wl + kDecodeWarps * kHeadsPerCta;                                    // [8]
